@@ -1,0 +1,566 @@
+// fusedmm_kernels.cuh -- device code of libfusedmm_b200 (sm_100a).
+//
+// The operation (HipGraph/FusedMM fusedMM.c:698-739): for every row u and every edge (u,v)
+//     T   = VOP(X_u, Y_v)          K-vector
+//     s   = ROP(X_u, T)  or a_uv   scalar
+//     out = SOP(s)                 scalar
+//     T   = VSC(out, T)            K-vector
+//     Z_u = AOP(Z_u, T)            K-vector
+// It is a gather-bound sparse contraction (about one flop per gathered byte), so the design goal is
+// bytes in flight, not tensor-core math:
+//   * one warp owns one row (or one fixed-size chunk of a long row) and keeps X_u and the Z_u
+//     accumulator in registers for the whole row;
+//   * the warp is cut into 32/G "edge slots" of G lanes; a slot gathers one neighbour row Y_v with
+//     NV 16-byte loads per lane (lane l of the slot reads vectors l, l+G, l+2G, ... so every load
+//     instruction covers one contiguous G*16-byte piece of the row), and U such gathers per slot are
+//     issued before the first one is consumed;
+//   * the 32 column ids of a batch are fetched with one coalesced load and handed out by shuffle;
+//   * ROP is a log2(G)-step shuffle reduction inside the slot, SOP/VSC/AOP run in registers, and no
+//     per-edge score is ever written to memory;
+//   * rows longer than `chunk` edges are cut into chunks that other warps process; their partial
+//     sums go to a scratch buffer and a small second kernel adds them in chunk order, so the result
+//     does not depend on scheduling (no floating-point atomics).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fmm {
+
+// stage codes = the nibbles of `imessage` (reference fusedMM.h:18-73)
+enum : int { VOP_NOOP = 0, VOP_COPY_LHS = 1, VOP_COPY_RHS = 2, VOP_ADD = 3, VOP_SUBL = 4, VOP_SUBR = 5,
+             VOP_MAX = 6, VOP_MIN = 7, OP_UDEF = 15 };
+enum : int { ROP_NOOP = 0, ROP_DOT = 1, ROP_ADD_LHS = 2, ROP_ADD_RHS = 3, ROP_NORML = 4, ROP_NORMR = 5 };
+enum : int { SOP_NOOP = 0, SOP_COPY = 1 };
+enum : int { VSC_NOOP = 0, VSC_MUL = 1, VSC_ADD = 2 };
+enum : int { AOP_NOOP = 0, AOP_ADD = 1, AOP_MAX = 2, AOP_MIN = 3 };
+enum : int { RT = -1 };  // "decided at run time": template value for the flag-interpreting kernel
+
+// scalar functions that SOP_UDEF can stand for (include/fusedmm_b200.h FUSEDMM_SOP_*)
+enum : int { SOPK_IDENTITY = 0, SOPK_SIGMOID = 1, SOPK_SIGMOID_TABLE_C = 2, SOPK_FR = 3, SOPK_TDIST = 4,
+             SOPK_TDIST_CLAMPED = 5, SOPK_LL = 6, SOPK_FA = 7, SOPK_AFFINE_RECIP = 8 };
+
+enum : int { MODE_ROWS = 0, MODE_HUB_CHUNKS = 1 };
+
+constexpr unsigned FULL = 0xffffffffu;
+constexpr int HUB_SHIFT = 40;  // packed counter: hub rows in the high 24 bits, chunks in the low 40
+constexpr unsigned long long HUB_CHUNK_MASK = (1ull << HUB_SHIFT) - 1ull;
+constexpr int SM_TABLE_SIZE = 2048;
+
+template <typename T>
+struct Params {
+   // CSR, four-array form (fusedMM.h:84-87); entry widths are run-time properties
+   const void *pntrb, *pntre, *indx;
+   const T *val;
+   const T *x, *y;
+   T *z;
+   long long m, k, ldx, ldy, ldz;
+   int ptr64, idx64;
+   int vop, rop, sop, vsc, aop;  // stage codes of this call
+   int sop_kind;                 // SOPK_* used when sop == OP_UDEF
+   T sp0, sp1, sp2;              // parameters of SOPK_AFFINE_RECIP
+   const T *sop_table;           // 2048-entry sigmoid table (SOPK_SIGMOID_TABLE_C)
+   int accumulate;               // 1: Z = AOP(Z, result)   0: Z = result
+   int mode;                     // MODE_ROWS | MODE_HUB_CHUNKS
+   long long chunk;              // rows with more edges than this are split
+   // hub-row scratch (written by scan_hub_rows, read by the chunk and fix-up passes)
+   unsigned long long *counter;  // packed (hub rows << 40) | chunks
+   long long *hub_row, *hub_base;
+   long long hub_cap, chunk_cap;
+   T *partials;                  // chunk_cap x k
+   // optional replication of the finished Z rows into other GPUs' Z buffers (multi-GPU all-gather
+   // fused into the epilogue); z_peer[i] has the same layout as z
+   int n_peers;
+   T *z_peer[8];
+};
+
+// ---------------------------------------------------------------------------------------------------
+// small helpers
+// ---------------------------------------------------------------------------------------------------
+template <int C>
+__device__ __forceinline__ int pick(int rt) { return C >= 0 ? C : rt; }
+
+__device__ __forceinline__ long long ld_index(const void *a, long long j, int is64)
+{
+   return is64 ? __ldg(reinterpret_cast<const long long *>(a) + j)
+               : static_cast<long long>(__ldg(reinterpret_cast<const int *>(a) + j));
+}
+
+__device__ __forceinline__ long long shfl_ll(long long v, int src)
+{
+   int lo = __shfl_sync(FULL, static_cast<int>(v), src);
+   int hi = __shfl_sync(FULL, static_cast<int>(v >> 32), src);
+   return (static_cast<long long>(hi) << 32) | static_cast<unsigned int>(lo);
+}
+
+template <typename T> struct VecOf;
+template <> struct VecOf<float>  { using type = float4;  static constexpr int W = 4; };
+template <> struct VecOf<double> { using type = double2; static constexpr int W = 2; };
+
+template <typename T>
+__device__ __forceinline__ void ld_vec_nc(const T *ptr, T (&out)[VecOf<T>::W]);
+template <>
+__device__ __forceinline__ void ld_vec_nc<float>(const float *ptr, float (&out)[4])
+{
+   float4 v = __ldg(reinterpret_cast<const float4 *>(ptr));
+   out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void ld_vec_nc<double>(const double *ptr, double (&out)[2])
+{
+   double2 v = __ldg(reinterpret_cast<const double2 *>(ptr));
+   out[0] = v.x; out[1] = v.y;
+}
+template <typename T>
+__device__ __forceinline__ void ld_vec(const T *ptr, T (&out)[VecOf<T>::W])
+{
+   using V = typename VecOf<T>::type;
+   V v = *reinterpret_cast<const V *>(ptr);
+   const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+   for (int i = 0; i < VecOf<T>::W; i++) out[i] = e[i];
+}
+template <typename T>
+__device__ __forceinline__ void st_vec(T *ptr, const T (&in)[VecOf<T>::W])
+{
+   using V = typename VecOf<T>::type;
+   V v;
+   T *e = reinterpret_cast<T *>(&v);
+#pragma unroll
+   for (int i = 0; i < VecOf<T>::W; i++) e[i] = in[i];
+   *reinterpret_cast<V *>(ptr) = v;
+}
+
+template <typename T> __device__ __forceinline__ T pos_inf();
+template <> __device__ __forceinline__ float  pos_inf<float>()  { return __int_as_float(0x7f800000); }
+template <> __device__ __forceinline__ double pos_inf<double>() { return __longlong_as_double(0x7ff0000000000000LL); }
+
+// ---------------------------------------------------------------------------------------------------
+// stage bodies.  lhs = X_u element, rhs = Y_v element.
+// ---------------------------------------------------------------------------------------------------
+// fusedMM.c:28-138.  SUBL is rhs-lhs (:87) and SUBR is lhs-rhs (:103); max/min use the reference's
+// comparison macros (fusedMM.c:18-19), not IEEE fmax/fmin.
+template <typename T>
+__device__ __forceinline__ T vop_apply(int vop, T lhs, T rhs)
+{
+   switch (vop) {
+      case VOP_COPY_LHS: return lhs;
+      case VOP_ADD:      return lhs + rhs;
+      case VOP_SUBL:     return rhs - lhs;
+      case VOP_SUBR:     return lhs - rhs;
+      case VOP_MAX:      return lhs > rhs ? lhs : rhs;
+      case VOP_MIN:      return lhs < rhs ? lhs : rhs;
+      default:           return rhs;  // VOP_COPY_RHS (and VOP_NOOP when the caller opted in)
+   }
+}
+// per-element term of the reduction; the second operand of ROP is T (fusedMM.c:725, :144-202)
+template <typename T>
+__device__ __forceinline__ T rop_term(int rop, T lhs, T t)
+{
+   switch (rop) {
+      case ROP_DOT:     return lhs * t;
+      case ROP_ADD_LHS: return lhs;
+      case ROP_ADD_RHS: return t;
+      case ROP_NORML:   return lhs * lhs;
+      default:          return t * t;  // ROP_NORMR
+   }
+}
+__host__ __device__ __forceinline__ bool vop_reads_x(int vop) { return vop != VOP_COPY_RHS && vop != VOP_NOOP; }
+__host__ __device__ __forceinline__ bool vop_reads_y(int vop) { return vop != VOP_COPY_LHS; }
+__host__ __device__ __forceinline__ bool rop_reads_x(int rop) { return rop == ROP_DOT || rop == ROP_ADD_LHS || rop == ROP_NORML; }
+
+// fusedMM.c:268-333
+template <typename T>
+__device__ __forceinline__ T aop_apply(int aop, T acc, T t)
+{
+   switch (aop) {
+      case AOP_MAX: return acc > t ? acc : t;
+      case AOP_MIN: return acc < t ? acc : t;
+      default:      return acc + t;
+   }
+}
+template <typename T>
+__device__ __forceinline__ T aop_identity(int aop)
+{
+   return aop == AOP_MAX ? -pos_inf<T>() : (aop == AOP_MIN ? pos_inf<T>() : T(0));
+}
+
+// Scalar functions.  fp32 uses expf/logf-class functions (a few ulp), never the fast intrinsics; the
+// table variant computes its index in double exactly as the host code it mirrors
+// (test/fusedMMtime.cpp:606-611).
+__device__ __forceinline__ float  fmm_exp(float v)  { return expf(v); }
+__device__ __forceinline__ double fmm_exp(double v) { return exp(v); }
+__device__ __forceinline__ float  fmm_sqrt(float v)  { return sqrtf(v); }
+__device__ __forceinline__ double fmm_sqrt(double v) { return sqrt(v); }
+__device__ __forceinline__ float  fmm_log2(float v)  { return log2f(v); }
+__device__ __forceinline__ double fmm_log2(double v) { return log2(v); }
+
+template <typename T>
+__device__ __forceinline__ T sop_udef(T s, int kind, T p0, T p1, T p2, const T *table)
+{
+   switch (kind) {
+      case SOPK_SIGMOID: return T(1) / (T(1) + fmm_exp(-s));
+      case SOPK_SIGMOID_TABLE_C: {
+         T sm;
+         if (s > T(5)) sm = T(1);
+         else if (s < T(-5)) sm = T(0);
+         else {
+            int idx = static_cast<int>((static_cast<double>(s) + 5.0) * SM_TABLE_SIZE / (2.0 * 5.0));
+            idx = idx > SM_TABLE_SIZE - 1 ? SM_TABLE_SIZE - 1 : idx;
+            sm = __ldg(table + idx);
+         }
+         return T(1) - sm;
+      }
+      case SOPK_FR:    return T(1) + T(1) / s;
+      case SOPK_TDIST: return T(1) / (T(1) + s);
+      case SOPK_TDIST_CLAMPED: {
+         T v = T(-2) / (T(1) + s);
+         return v > T(5) ? T(5) : (v < T(-5) ? T(-5) : v);
+      }
+      case SOPK_LL: return fmm_log2(T(1) + fmm_sqrt(s));
+      case SOPK_FA: return fmm_sqrt(s) + T(1) / s;
+      case SOPK_AFFINE_RECIP: {
+         T v = p0 / (p1 + s);
+         if (p2 > T(0)) v = v > p2 ? p2 : (v < -p2 ? -p2 : v);
+         return v;
+      }
+      default: return s;
+   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Work-item lookup shared by the two main kernels.
+// ---------------------------------------------------------------------------------------------------
+struct WorkItem {
+   long long row, eb, ee;  // row and edge range [eb, ee)
+   long long dst_item;     // chunk index for MODE_HUB_CHUNKS, -1 for a whole row
+};
+
+// largest slot with hub_base[slot] <= item; hub_base is increasing because slot and base come out of
+// one packed atomic counter
+__device__ __forceinline__ long long hub_slot_of(const long long *hub_base, long long nh, long long item)
+{
+   long long lo = 0, hi = nh - 1;
+   while (lo < hi) {
+      long long mid = (lo + hi + 1) >> 1;
+      if (__ldg(hub_base + mid) <= item) lo = mid; else hi = mid - 1;
+   }
+   return lo;
+}
+
+template <typename T>
+__device__ __forceinline__ bool chunk_item(const Params<T> &p, long long item, long long nh, WorkItem &w)
+{
+   long long slot = hub_slot_of(p.hub_base, nh, item);
+   w.row = __ldg(p.hub_row + slot);
+   long long c = item - __ldg(p.hub_base + slot);
+   long long pb = ld_index(p.pntrb, w.row, p.ptr64), pe = ld_index(p.pntre, w.row, p.ptr64);
+   w.eb = pb + c * p.chunk;
+   w.ee = w.eb + p.chunk < pe ? w.eb + p.chunk : pe;
+   w.dst_item = item;
+   return true;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Vector engine: one warp, one work item, K <= G*NV*W elements, everything 16-byte aligned.
+// ---------------------------------------------------------------------------------------------------
+template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U>
+struct VecEngine {
+   static constexpr int W = VecOf<T>::W;
+   static constexpr int S = 32 / G;  // edge slots per warp
+   static_assert(S * U <= 32 && (32 % (S * U)) == 0, "S*U must divide 32");
+
+   __device__ __forceinline__ static void run(const Params<T> &p, const WorkItem &w, int lane,
+                                              T (&acc)[NV][W])
+   {
+      const int vop = pick<VOPC>(p.vop), rop = pick<ROPC>(p.rop), vsc = pick<VSCC>(p.vsc),
+                aop = pick<AOPC>(p.aop);
+      const int lg = lane % G, slot = lane / G;
+      const bool need_x = vop_reads_x(vop) || rop_reads_x(rop);
+      const bool need_y = vop_reads_y(vop);
+      const bool use_val = (rop == ROP_NOOP) && (vsc != VSC_NOOP);
+      const bool use_sop_udef = (p.sop == OP_UDEF);
+
+      bool inb[NV];
+      T xv[NV][W];
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+         const long long e0 = static_cast<long long>(v * G + lg) * W;
+         inb[v] = e0 < p.k;
+#pragma unroll
+         for (int i = 0; i < W; i++) { xv[v][i] = T(0); acc[v][i] = aop_identity<T>(aop); }
+         if (need_x && inb[v]) ld_vec(p.x + w.row * p.ldx + e0, xv[v]);
+      }
+
+      for (long long base = w.eb; base < w.ee; base += 32) {
+         const long long j = base + lane;
+         const long long my_cid = (j < w.ee && need_y) ? ld_index(p.indx, j, p.idx64) : 0;
+         const T my_val = (use_val && j < w.ee) ? __ldg(p.val + j) : T(0);
+         const int nb = (w.ee - base) < 32 ? static_cast<int>(w.ee - base) : 32;
+#pragma unroll 1
+         for (int t = 0; t < nb; t += S * U) {
+            T yv[U][NV][W];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+               const int e = t + u * S + slot;  // < 32 because S*U divides 32
+               ok[u] = e < nb;
+               const long long cid = p.idx64 ? shfl_ll(my_cid, e)
+                                             : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e));
+               const T *yrow = p.y + cid * p.ldy;
+#pragma unroll
+               for (int v = 0; v < NV; v++) {
+#pragma unroll
+                  for (int i = 0; i < W; i++) yv[u][v][i] = T(0);
+                  if (need_y && ok[u] && inb[v]) ld_vec_nc(yrow + static_cast<long long>(v * G + lg) * W, yv[u][v]);
+               }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+               const int e = t + u * S + slot;
+               T tv[NV][W];
+               T s = T(0);
+#pragma unroll
+               for (int v = 0; v < NV; v++)
+#pragma unroll
+                  for (int i = 0; i < W; i++) {
+                     tv[v][i] = vop_apply(vop, xv[v][i], yv[u][v][i]);
+                     if (rop != ROP_NOOP) s += rop_term(rop, xv[v][i], tv[v][i]);
+                  }
+               if (rop != ROP_NOOP) {
+#pragma unroll
+                  for (int off = G / 2; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
+               } else {
+                  s = __shfl_sync(FULL, my_val, e);
+               }
+               const T out = use_sop_udef ? sop_udef(s, p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : s;
+               if (ok[u]) {
+#pragma unroll
+                  for (int v = 0; v < NV; v++)
+#pragma unroll
+                     for (int i = 0; i < W; i++) {
+                        T tt = tv[v][i];
+                        if (vsc == VSC_MUL) tt = out * tt;
+                        else if (vsc == VSC_ADD) tt = out + tt;
+                        acc[v][i] = aop_apply(aop, acc[v][i], tt);
+                     }
+               }
+            }
+         }
+      }
+      // combine the edge slots: afterwards every slot holds the row's result
+#pragma unroll
+      for (int off = G; off < 32; off <<= 1)
+#pragma unroll
+         for (int v = 0; v < NV; v++)
+#pragma unroll
+            for (int i = 0; i < W; i++)
+               acc[v][i] = aop_apply(aop, acc[v][i], __shfl_xor_sync(FULL, acc[v][i], off));
+   }
+};
+
+constexpr int WARPS_PER_CTA = 8;
+
+// One warp per row (MODE_ROWS) or a grid-stride loop over the chunks of split rows
+// (MODE_HUB_CHUNKS).  Rows longer than p.chunk are skipped in MODE_ROWS.
+template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+fused_vec_kernel(const Params<T> p)
+{
+   using Eng = VecEngine<T, VOPC, ROPC, VSCC, AOPC, G, NV, U>;
+   constexpr int W = Eng::W;
+   const int lane = threadIdx.x & 31;
+   const int aop = pick<AOPC>(p.aop);
+   long long wid = static_cast<long long>(blockIdx.x) * WARPS_PER_CTA + (threadIdx.x >> 5);
+   const long long stride = static_cast<long long>(gridDim.x) * WARPS_PER_CTA;
+   long long nh = 0, nchunks = 0;
+   if (p.mode == MODE_HUB_CHUNKS) {
+      const unsigned long long c = *p.counter;
+      nh = static_cast<long long>(c >> HUB_SHIFT);
+      nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
+      if (nh > p.hub_cap || nchunks > p.chunk_cap) return;  // scratch too small: the host enlarges it and reruns
+   }
+   for (;; wid += stride) {
+      WorkItem w;
+      if (p.mode == MODE_ROWS) {
+         if (wid >= p.m) return;
+         w.row = wid;
+         w.eb = ld_index(p.pntrb, wid, p.ptr64);
+         w.ee = ld_index(p.pntre, wid, p.ptr64);
+         w.dst_item = -1;
+         if (w.ee - w.eb > p.chunk) return;
+      } else {
+         if (wid >= nchunks) return;
+         chunk_item(p, wid, nh, w);
+      }
+      T acc[NV][W];
+      Eng::run(p, w, lane, acc);
+
+      if (lane < G) {  // slot 0 holds (like every slot) the finished sums
+         const bool to_z = w.dst_item < 0;
+         T *dst = to_z ? p.z + w.row * p.ldz : p.partials + w.dst_item * p.k;
+#pragma unroll
+         for (int v = 0; v < NV; v++) {
+            const long long e0 = static_cast<long long>(v * G + lane) * W;
+            if (e0 < p.k) {
+               if (to_z && p.accumulate) {
+                  T old[W];
+                  ld_vec(dst + e0, old);
+#pragma unroll
+                  for (int i = 0; i < W; i++) acc[v][i] = aop_apply(aop, old[i], acc[v][i]);
+               }
+               st_vec(dst + e0, acc[v]);
+               if (to_z) {
+                  for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
+               }
+            }
+         }
+      }
+      if (p.mode == MODE_ROWS) return;
+   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Element-strided engine: any K, any leading dimension, any alignment; all stage codes at run time.
+// Lane l owns elements l, l+32, ... of a 32*EPT-element tile of K; a message with a reduction walks
+// the whole K once per edge and per tile to get s.  It exists so that every legal call has a GPU
+// path; the vector engine is the fast one.
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+fused_any_kernel(const Params<T> p)
+{
+   constexpr int EPT = 8;
+   const int lane = threadIdx.x & 31;
+   const int vop = p.vop, rop = p.rop, vsc = p.vsc, aop = p.aop;
+   const bool need_y = vop_reads_y(vop);
+   const bool use_val = (rop == ROP_NOOP) && (vsc != VSC_NOOP);
+   const bool use_sop_udef = (p.sop == OP_UDEF);
+   long long wid = static_cast<long long>(blockIdx.x) * WARPS_PER_CTA + (threadIdx.x >> 5);
+   const long long stride = static_cast<long long>(gridDim.x) * WARPS_PER_CTA;
+   long long nh = 0, nchunks = 0;
+   if (p.mode == MODE_HUB_CHUNKS) {
+      const unsigned long long c = *p.counter;
+      nh = static_cast<long long>(c >> HUB_SHIFT);
+      nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
+      if (nh > p.hub_cap || nchunks > p.chunk_cap) return;
+   }
+   for (;; wid += stride) {
+      WorkItem w;
+      if (p.mode == MODE_ROWS) {
+         if (wid >= p.m) return;
+         w.row = wid;
+         w.eb = ld_index(p.pntrb, wid, p.ptr64);
+         w.ee = ld_index(p.pntre, wid, p.ptr64);
+         w.dst_item = -1;
+         if (w.ee - w.eb > p.chunk) return;
+      } else {
+         if (wid >= nchunks) return;
+         chunk_item(p, wid, nh, w);
+      }
+      const T *xr = p.x + w.row * p.ldx;  // dereferenced only when a stage reads X
+      const bool to_z = w.dst_item < 0;
+      T *dst = to_z ? p.z + w.row * p.ldz : p.partials + w.dst_item * p.k;
+      const bool need_x = vop_reads_x(vop) || rop_reads_x(rop);
+
+      for (long long kt = 0; kt < p.k; kt += 32 * EPT) {
+         T acc[EPT];
+#pragma unroll
+         for (int e = 0; e < EPT; e++) acc[e] = aop_identity<T>(aop);
+         for (long long j = w.eb; j < w.ee; j++) {
+            const long long cid = need_y ? ld_index(p.indx, j, p.idx64) : 0;
+            const T *yr = p.y + cid * p.ldy;
+            T s;
+            if (rop != ROP_NOOP) {
+               s = T(0);
+               for (long long t = lane; t < p.k; t += 32) {
+                  const T xe = need_x ? xr[t] : T(0);
+                  const T ye = need_y ? __ldg(yr + t) : T(0);
+                  s += rop_term(rop, xe, vop_apply(vop, xe, ye));
+               }
+#pragma unroll
+               for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
+            } else {
+               s = use_val ? __ldg(p.val + j) : T(0);
+            }
+            const T out = use_sop_udef ? sop_udef(s, p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : s;
+#pragma unroll
+            for (int e = 0; e < EPT; e++) {
+               const long long t = kt + e * 32 + lane;
+               if (t < p.k) {
+                  const T xe = need_x ? xr[t] : T(0);
+                  const T ye = need_y ? __ldg(yr + t) : T(0);
+                  T tt = vop_apply(vop, xe, ye);
+                  if (vsc == VSC_MUL) tt = out * tt;
+                  else if (vsc == VSC_ADD) tt = out + tt;
+                  acc[e] = aop_apply(aop, acc[e], tt);
+               }
+            }
+         }
+#pragma unroll
+         for (int e = 0; e < EPT; e++) {
+            const long long t = kt + e * 32 + lane;
+            if (t < p.k) {
+               T r = acc[e];
+               if (to_z && p.accumulate) r = aop_apply(aop, dst[t], r);
+               dst[t] = r;
+               if (to_z)
+                  for (int q = 0; q < p.n_peers; q++) p.z_peer[q][w.row * p.ldz + t] = r;
+            }
+         }
+      }
+      if (p.mode == MODE_ROWS) return;
+   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Row scheduler, device side.
+// ---------------------------------------------------------------------------------------------------
+// Pass 1: find the rows that have more than `chunk` edges.  Each gets a slot in the hub list and a
+// contiguous run of ceil(deg/chunk) chunk indices, both taken from ONE packed atomic so that
+// hub_base[] is increasing in the slot number.
+__global__ void scan_hub_rows(const void *pntrb, const void *pntre, int ptr64, long long m,
+                              long long chunk, unsigned long long *counter, long long *hub_row,
+                              long long *hub_base, long long hub_cap);
+
+// Pass 3: for every split row, Z_row = AOP(old Z_row or identity, partial_0, partial_1, ...) in chunk
+// order.  One warp per split row, lanes strided over K.
+template <typename T>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+hub_fixup_kernel(const Params<T> p)
+{
+   const int lane = threadIdx.x & 31;
+   const unsigned long long c = *p.counter;
+   const long long nh = static_cast<long long>(c >> HUB_SHIFT);
+   const long long nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
+   if (nh > p.hub_cap || nchunks > p.chunk_cap) return;
+   const long long stride = static_cast<long long>(gridDim.x) * WARPS_PER_CTA;
+   for (long long slot = static_cast<long long>(blockIdx.x) * WARPS_PER_CTA + (threadIdx.x >> 5); slot < nh;
+        slot += stride) {
+      const long long row = p.hub_row[slot], base = p.hub_base[slot];
+      const long long deg = ld_index(p.pntre, row, p.ptr64) - ld_index(p.pntrb, row, p.ptr64);
+      const long long nch = (deg + p.chunk - 1) / p.chunk;
+      T *zr = p.z + row * p.ldz;
+      for (long long t = lane; t < p.k; t += 32) {
+         T a = p.accumulate ? zr[t] : aop_identity<T>(p.aop);
+         for (long long q = 0; q < nch; q++) a = aop_apply(p.aop, a, p.partials[(base + q) * p.k + t]);
+         zr[t] = a;
+         for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = a;
+      }
+   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Host-side launch table (defined in the per-pattern translation units).
+// ---------------------------------------------------------------------------------------------------
+enum : int { PAT_GENERIC = 0, PAT_SIGMOID = 1, PAT_TDIST = 2, PAT_SPMM = 3, PAT_GCN = 4 };
+
+// Launches fused_vec_kernel<T, pattern ops, G, NV, U> with `grid` CTAs on `stream`.
+// Returns false when that (G, NV) tiling is not instantiated.
+template <typename T>
+bool launch_vec(int pattern, int G, int NV, const Params<T> &p, long long grid, cudaStream_t stream);
+template <typename T>
+void launch_any(const Params<T> &p, long long grid, cudaStream_t stream);
+template <typename T>
+void launch_fixup(const Params<T> &p, long long grid, cudaStream_t stream);
+
+}  // namespace fmm

@@ -1,0 +1,243 @@
+/*
+ * fusedmm_b200.h -- C ABI of libfusedmm_b200.so
+ *
+ * A from-scratch sm_100a (NVIDIA B200) implementation of the FusedMM operation
+ *
+ *     Z_u  =  AOP_v ( VSC( SOP( ROP( X_u, VOP(X_u, Y_v) ) or a_uv ), VOP(X_u, Y_v) ) )   for every edge (u,v) of a CSR matrix
+ *
+ * behind the entry point of HipGraph/FusedMM.  Every function below is `extern "C"`, takes plain
+ * pointers and integer sizes and no CUDA or torch types, so that C host code (and cgo / JNI / ctypes
+ * bindings) can call it.  Each declaration cites the reference interface it replaces as
+ * `file:line` inside the HipGraph/FusedMM source tree.
+ *
+ * Pointer residency.  The reference only sees host memory.  Here every array argument may
+ * independently be a device pointer (used in place, nothing is copied) or a host pointer (staged to the
+ * GPU for the call; Z is copied back before the call returns).  Residency is detected per pointer
+ * with cudaPointerGetAttributes.  Unless stated otherwise a call is synchronous: Z is complete when
+ * it returns, exactly like the reference.
+ *
+ * There is no CPU implementation in this library.  If no CUDA device is usable every entry point
+ * returns FUSEDMM_B200_ERR_CUDA.
+ */
+#ifndef FUSEDMM_B200_H
+#define FUSEDMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------
+ * Status codes.  Non-negative values are the reference's (fusedMM.h:103-112) and keep their
+ * meaning; negative values below -1 are new and report CUDA-side failures.
+ * ---------------------------------------------------------------------------------------------- */
+#define FUSEDMM_B200_OK                  0    /* FUSEDMM_SUCCESS_RETURN            fusedMM.h:103 */
+#define FUSEDMM_B200_ERR_VOP             2    /* FUSEDMM_VOP_FAIL_RETURN           fusedMM.h:105 */
+#define FUSEDMM_B200_ERR_ROP             4    /* FUSEDMM_ROP_FAIL_RETURN           fusedMM.h:106 */
+#define FUSEDMM_B200_ERR_AOP             8    /* FUSEDMM_AOP_FAIL_RETURN           fusedMM.h:107 */
+#define FUSEDMM_B200_ERR_SOP             16   /* FUSEDMM_SOP_FAIL_RETURN           fusedMM.h:108 */
+#define FUSEDMM_B200_ERR_VSC             32   /* FUSEDMM_VSC_FAIL_RETURN           fusedMM.h:109 */
+#define FUSEDMM_B200_ERR_NOMEM          (-1)  /* FUSEDMM_NOT_ENOUGH_MEM            fusedMM.h:110 */
+#define FUSEDMM_B200_ERR_UDEF            64   /* FUSEDMM_UNDEFINED_USER_FUNCTION   fusedMM.h:111 */
+#define FUSEDMM_B200_ERR_NO_OPT          128  /* FUSEDMM_NO_OPT_IMPL               fusedMM.h:112 */
+#define FUSEDMM_B200_ERR_CUDA           (-2)  /* a CUDA runtime call failed, or no device            */
+#define FUSEDMM_B200_ERR_ARG            (-3)  /* negative size, ld < k, null pointer that is needed  */
+#define FUSEDMM_B200_ERR_LIMIT          (-4)  /* a fixed capacity was exceeded (see the entry point) */
+
+/* ------------------------------------------------------------------------------------------------
+ * Scalar operations (SOP) that can run on the device.
+ *
+ * The reference resolves SOP_UDEF to a host function `int SOP_UDEF_FUNC(VALUETYPE, VALUETYPE*)`
+ * linked by the caller (fusedMM.h:139) and calls it once per edge (fusedMM.c:729).  A GPU kernel
+ * cannot call a host function, so the bodies the reference's own tester links
+ * (test/fusedMMtime.cpp:625-674) plus the two that the benchmark configurations name are built in.
+ * Which one SOP_UDEF means is chosen, in this order, by
+ *   1. an explicit `fusedmm_b200_sop` passed to fusedmm_b200_csr();
+ *   2. a host SOP_UDEF_FUNC pointer passed to a *_udef entry point: it is evaluated on the host at a
+ *      fixed set of sample points and matched against the built-ins (no match -> status 64);
+ *   3. the process-wide default set with fusedmm_b200_set_sop() (initially SIGMOID).
+ * ---------------------------------------------------------------------------------------------- */
+#define FUSEDMM_SOP_IDENTITY        0  /* out = s                      default body, fusedMMtime.cpp:669-673 */
+#define FUSEDMM_SOP_SIGMOID         1  /* out = 1/(1+exp(-s))                                               */
+#define FUSEDMM_SOP_SIGMOID_TABLE_C 2  /* out = 1 - table_sigmoid(s)   fusedMMtime.cpp:586-611, :628-632     */
+#define FUSEDMM_SOP_FR              3  /* out = 1 + 1/s                fusedMMtime.cpp:635-639               */
+#define FUSEDMM_SOP_TDIST           4  /* out = 1/(1+s)                                                     */
+#define FUSEDMM_SOP_TDIST_CLAMPED   5  /* out = clamp(-2/(1+s), +-5)   fusedMMtime.cpp:612-617, :642-646     */
+#define FUSEDMM_SOP_LL              6  /* out = log2(1+sqrt(s))        fusedMMtime.cpp:649-653               */
+#define FUSEDMM_SOP_FA              7  /* out = sqrt(s) + 1/s          fusedMMtime.cpp:656-660               */
+#define FUSEDMM_SOP_AFFINE_RECIP    8  /* out = clamp(p0/(p1+s), +-p2) when p2>0, else p0/(p1+s)            */
+#define FUSEDMM_SOP_KIND_COUNT      9
+
+typedef struct fusedmm_b200_sop {
+   int32_t kind;      /* one of FUSEDMM_SOP_*                                  */
+   int32_t reserved;  /* must be 0                                             */
+   double  p0, p1, p2;/* parameters of FUSEDMM_SOP_AFFINE_RECIP, else ignored  */
+} fusedmm_b200_sop;
+
+int fusedmm_b200_set_sop(int32_t kind, double p0, double p1, double p2);
+int fusedmm_b200_get_sop(fusedmm_b200_sop *out);
+
+/* ------------------------------------------------------------------------------------------------
+ * fusedMM_csr, one symbol per (VALUETYPE, INDEXTYPE) build of the reference.
+ *
+ * Replaces: int fusedMM_csr(imessage, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pntre,
+ *                           x, ldx, y, ldy, beta, z, ldz)        fusedMM.h:76-97, fusedMM.c:487-744
+ * Argument meaning, order and the return codes are the reference's.  As in the reference `alpha`,
+ * `n`, `nnz`, `rows` and `cols` are not read; `m` rows are processed.  `beta == 0` overwrites Z (rows
+ * without edges become 0), any other beta accumulates into Z, which is the behaviour of the
+ * reference's optimised kernels (kernels/src/kernels.c:501-520); see fusedmm_b200_set_option
+ * ("beta_mode") for the general kernel's behaviour.
+ *
+ * The reference compiles one function named fusedMM_csr per choice of the VALUETYPE and INDEXTYPE
+ * macros; a shared library cannot export four ABIs under one name, so the symbols carry the types
+ * (s|d = float|double, i32|i64 = INDEXTYPE) and include/fusedMM.h maps the reference's name onto
+ * the one that matches the caller's macros.
+ * ---------------------------------------------------------------------------------------------- */
+#define FUSEDMM_B200_DECL_CSR(NAME, VT, IT)                                                        \
+   int NAME(const int32_t imessage, const IT m, const IT n, const IT k, const VT alpha,            \
+            const IT nnz, const IT rows, const IT cols, const VT *val, const IT *indx,             \
+            const IT *pntrb, const IT *pntre, const VT *x, const IT ldx, const VT *y,              \
+            const IT ldy, const VT beta, VT *z, const IT ldz)
+
+FUSEDMM_B200_DECL_CSR(sfusedMM_csr_i32, float,  int32_t);
+FUSEDMM_B200_DECL_CSR(sfusedMM_csr_i64, float,  int64_t);
+FUSEDMM_B200_DECL_CSR(dfusedMM_csr_i32, double, int32_t);
+FUSEDMM_B200_DECL_CSR(dfusedMM_csr_i64, double, int64_t);
+
+/* The reference's default build (VALUETYPE float, INDEXTYPE int64_t; kernels/CONFIG/make.base:151,155)
+ * is also exported under the reference's own symbol name `fusedMM_csr`, for objects that were
+ * compiled against the reference's header with exactly those types and are only re-linked.  It is
+ * declared here on request only, because include/fusedMM.h defines that name as a macro. */
+#if defined(FUSEDMM_B200_DECLARE_REFERENCE_SYMBOL) && !defined(fusedMM_csr)
+FUSEDMM_B200_DECL_CSR(fusedMM_csr, float, int64_t);
+#endif
+
+/* Same call with the caller's host SOP_UDEF_FUNC (fusedMM.h:139) handed over explicitly; used by
+ * the fusedMM_csr wrapper of include/fusedMM.h.  `sop_udef` may be NULL. */
+#define FUSEDMM_B200_DECL_CSR_UDEF(NAME, VT, IT)                                                   \
+   int NAME(const int32_t imessage, const IT m, const IT n, const IT k, const VT alpha,            \
+            const IT nnz, const IT rows, const IT cols, const VT *val, const IT *indx,             \
+            const IT *pntrb, const IT *pntre, const VT *x, const IT ldx, const VT *y,              \
+            const IT ldy, const VT beta, VT *z, const IT ldz, int (*sop_udef)(VT, VT *))
+
+FUSEDMM_B200_DECL_CSR_UDEF(sfusedMM_csr_i32_udef, float,  int32_t);
+FUSEDMM_B200_DECL_CSR_UDEF(sfusedMM_csr_i64_udef, float,  int64_t);
+FUSEDMM_B200_DECL_CSR_UDEF(dfusedMM_csr_i32_udef, double, int32_t);
+FUSEDMM_B200_DECL_CSR_UDEF(dfusedMM_csr_i64_udef, double, int64_t);
+
+/* Mixed index widths: 64-bit row pointers and sizes with 32-bit column ids.  The reference has a
+ * single INDEXTYPE (fusedMM.h:79-96) and cannot express this; it is what a graph with more than
+ * 2^31 edges but fewer than 2^31 vertices wants. */
+int sfusedMM_csr_p64i32(const int32_t imessage, const int64_t m, const int64_t n, const int64_t k,
+                        const float alpha, const int64_t nnz, const int64_t rows, const int64_t cols,
+                        const float *val, const int32_t *indx, const int64_t *pntrb,
+                        const int64_t *pntre, const float *x, const int64_t ldx, const float *y,
+                        const int64_t ldy, const float beta, float *z, const int64_t ldz);
+int dfusedMM_csr_p64i32(const int32_t imessage, const int64_t m, const int64_t n, const int64_t k,
+                        const double alpha, const int64_t nnz, const int64_t rows, const int64_t cols,
+                        const double *val, const int32_t *indx, const int64_t *pntrb,
+                        const int64_t *pntre, const double *x, const int64_t ldx, const double *y,
+                        const int64_t ldy, const double beta, double *z, const int64_t ldz);
+
+/* ------------------------------------------------------------------------------------------------
+ * The optimised-kernel dispatcher, callable directly.
+ * Replaces: void sgfusedMM_csr / dgfusedMM_csr (const char tkern, ...)   kernels/include/kernels.h:17-37,
+ *           kernels/src/kernels.c:456-631.   tkern: 't' t-dist/FR, 's' sigmoid, 'm' SpMM, 'g' GCN.
+ * Like the reference they return nothing; an unknown letter prints a message to stderr.  The SOP for
+ * 't' and 's' is the process-wide default (fusedmm_b200_set_sop).
+ * ---------------------------------------------------------------------------------------------- */
+#define FUSEDMM_B200_DECL_G(NAME, VT, IT)                                                          \
+   void NAME(const char tkern, const IT m, const IT n, const IT k, const VT alpha, const IT nnz,   \
+             const IT rows, const IT cols, const VT *val, const IT *indx, const IT *pntrb,         \
+             const IT *pntre, const VT *A, const IT lda, const VT *B, const IT ldb, const VT beta, \
+             VT *C, const IT ldc)
+
+FUSEDMM_B200_DECL_G(sgfusedMM_csr_i32, float,  int32_t);
+FUSEDMM_B200_DECL_G(sgfusedMM_csr_i64, float,  int64_t);
+FUSEDMM_B200_DECL_G(dgfusedMM_csr_i32, double, int32_t);
+FUSEDMM_B200_DECL_G(dgfusedMM_csr_i64, double, int64_t);
+
+/* ------------------------------------------------------------------------------------------------
+ * The one function all of the above funnel into.
+ *
+ *   dtype     0 = float, 1 = double                       (VALUETYPE, fusedMM.c:9-13)
+ *   ptr_bits  32 or 64: width of pntrb / pntre entries
+ *   idx_bits  32 or 64: width of indx entries             (INDEXTYPE, fusedMM.h:79-96)
+ *   sop       NULL = process-wide default
+ *   stream    NULL = run on the library's own stream and return when Z is complete.
+ *             Otherwise a cudaStream_t: all work is enqueued on it and the call returns without
+ *             waiting; every array must then be a device pointer (else FUSEDMM_B200_ERR_ARG), and
+ *             a capacity overflow of the hub-row scratch is reported by the next synchronous call
+ *             or by fusedmm_b200_stream_status().
+ * Everything else: as fusedMM_csr (fusedMM.h:76-97).
+ * ---------------------------------------------------------------------------------------------- */
+int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage,
+                     int64_t m, int64_t n, int64_t k, double alpha, int64_t nnz, int64_t rows,
+                     int64_t cols, const void *val, const void *indx, const void *pntrb,
+                     const void *pntre, const void *x, int64_t ldx, const void *y, int64_t ldy,
+                     double beta, void *z, int64_t ldz, const fusedmm_b200_sop *sop, void *stream);
+
+/* After work enqueued with a non-NULL stream has completed: 0, or FUSEDMM_B200_ERR_LIMIT when the
+ * hub-row scratch was too small for that call (the scratch has then been enlarged; run the call again). */
+int fusedmm_b200_stream_status(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Row scheduler pieces that are useful on their own.
+ *
+ * fusedmm_b200_shard_rows_*: cut rows [0,m) into `nshards` contiguous ranges of (nearly) equal edge
+ * count: bounds[g] .. bounds[g+1] is shard g, bounds has nshards+1 entries.  This lifts the idea of
+ * the reference's per-thread partition (fusedMM.c:633-676; rows are never split) from OpenMP threads
+ * to GPUs.  pntrb/pntre are HOST pointers here.  A shard is then computed with an ordinary
+ * fusedMM_csr call on (m = bounds[g+1]-bounds[g], pntrb + bounds[g], pntre + bounds[g],
+ * x + bounds[g]*ldx, z + bounds[g]*ldz): the four-array CSR needs no re-basing.
+ * ---------------------------------------------------------------------------------------------- */
+int fusedmm_b200_shard_rows_i32(int64_t m, int32_t nshards, const int32_t *pntrb,
+                                const int32_t *pntre, int64_t *bounds);
+int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb,
+                                const int64_t *pntre, int64_t *bounds);
+
+/* ------------------------------------------------------------------------------------------------
+ * Options, introspection, teardown.
+ *
+ * fusedmm_b200_set_option(name, value) -> 0, or FUSEDMM_B200_ERR_ARG for an unknown name/value:
+ *   "beta_mode"      0 (default): the four patterns the reference has optimised kernels for honour
+ *                    beta (0 = overwrite) and every other message accumulates into Z, i.e. a build of
+ *                    the reference with ENABLE_OPT_FUSEDMM (fusedMM.c:512-605);
+ *                    1: every message accumulates into Z whatever beta is, i.e. the reference's
+ *                    general kernel (fusedMM.c:698-739).
+ *   "accept_vop_noop" 0 (default): VOP_NOOP returns status 2 as in the reference (fusedMM.c:346-377);
+ *                    1: VOP_NOOP means T = Y_v.
+ *   "hub_chunk"      edges per work item for rows that are split across warps (default 512).
+ *   "force_tiling"   0 = automatic; otherwise (lanes_per_edge << 8) | vectors_per_lane.
+ *   "force_generic"  1 = run every message through the flag-interpreting kernel.
+ * fusedmm_b200_get_option(name, &value) reads them back.
+ * ---------------------------------------------------------------------------------------------- */
+int fusedmm_b200_set_option(const char *name, int64_t value);
+int fusedmm_b200_get_option(const char *name, int64_t *value);
+
+/* Kernels launched / bytes copied by the most recent call on the calling thread. */
+typedef struct fusedmm_b200_call_info {
+   int32_t kernel_launches;   /* CUDA kernels of this library launched by the call           */
+   int32_t pattern;           /* 0 generic, 1 sigmoid-like, 2 tdist/FR-like, 3 SpMM, 4 GCN   */
+   int32_t lanes_per_edge;    /* tiling that was chosen; 0 = element-strided fallback        */
+   int32_t vectors_per_lane;
+   int64_t h2d_bytes;         /* staged host->device bytes                                   */
+   int64_t d2h_bytes;         /* device->host bytes (Z)                                      */
+   int64_t hub_rows;          /* rows split across several warps                             */
+   int64_t hub_chunks;        /* partial-row work items                                      */
+   float   device_ms;         /* CUDA-event time of the kernels of a synchronous call        */
+   int32_t sop_kind;          /* SOP that ran                                                */
+} fusedmm_b200_call_info;
+int fusedmm_b200_last_call_info(fusedmm_b200_call_info *out);
+
+const char *fusedmm_b200_status_string(int status);
+const char *fusedmm_b200_version(void);
+
+/* Frees every device buffer the library holds (staging copies, hub-row scratch). */
+int fusedmm_b200_release(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSEDMM_B200_H */

@@ -1,0 +1,371 @@
+"""Parity of the CUDA path with the reference, through the C ABI, on a GPU.
+
+Every comparison is against the CPU oracle (pinned to the reference in test_oracle_pin.py), against the
+golden outputs of the reference itself, or -- at full benchmark size -- against properties that do not
+need a CPU pass.  Tolerances: 1e-4 (float32) and 1e-10 (float64) in the metric of cases.rel_err.
+"""
+import ctypes
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from cases import MESSAGES, RTOL, dense, random_csr, rel_err
+from fusedmm_b200 import api, messages as M, synth
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).parent / "golden" / "reference_general_kernel.npz"
+
+
+def dev(a, device):
+    import torch
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+def run_gpu(device, msg, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz, sop=None):
+    """device-resident call; returns (status, Z as numpy)."""
+    import torch
+    t = [dev(a, device) for a in (val, indx, pntrb, pntre, x, y, z)]
+    st = api.fusedMM_csr(msg, m, n, k, 1.0, 0, m, n, t[0], t[1], t[2], t[3], t[4], ldx, t[5], ldy, beta,
+                         t[6], ldz, sop=sop)
+    torch.cuda.synchronize()
+    return st, t[6].cpu().numpy()
+
+
+def sop_for(name):
+    return {"sigmoid": M.SOP_SIGMOID, "tdist": M.SOP_TDIST, "subl_norml_udef_mul_max": M.SOP_TDIST,
+            "copyrhs_dot_udef_mul_add_fr": M.SOP_SIGMOID_TABLE_C}.get(name, M.SOP_IDENTITY)
+
+
+def test_library_is_loaded_and_reports_itself(cuda_device):
+    assert b"sm_100a" in api.lib().fusedmm_b200_version()
+
+
+def test_golden_outputs_of_the_reference(cuda_device):
+    data = np.load(GOLDEN)
+    keys = sorted({k.split("_")[0] for k in data.files})
+    assert len(keys) == 44
+    engines = set()
+    for key in keys:
+        msg, m, n, k, ld, sop = (int(v) for v in data[key + "_meta"])
+        want = data[key + "_z"]
+        st, z = run_gpu(cuda_device, msg, m, n, k, data[key + "_val"], data[key + "_indx"],
+                        data[key + "_pntrb"], data[key + "_pntre"], data[key + "_x"], ld, data[key + "_y"],
+                        ld, 0.0, np.zeros_like(want), ld, sop=sop)
+        assert st == 0
+        engines.add(api.call_info().lanes_per_edge)
+        assert rel_err(z, want, k) <= RTOL[want.dtype], (key, str(data[key + "_name"]))
+        assert (z[:, k:] == 0).all()  # padding columns are not written
+    assert 0 in engines and len(engines) > 1  # both the vector engine and the element-strided one ran
+
+
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+@pytest.mark.parametrize("name", list(MESSAGES))
+def test_every_message_against_the_oracle(cuda_device, oracle, vt, name):
+    msg = MESSAGES[name]
+    rng = np.random.default_rng(abs(hash((name, vt.__name__))) % 2**31)
+    m, n = 1500, 1100
+    for k, it, pt in ((4, np.int32, np.int32), (32, np.int64, np.int64), (64, np.int32, np.int64),
+                      (96, np.int32, np.int32), (128, np.int64, np.int64), (200, np.int32, np.int32),
+                      (256, np.int32, np.int64), (30, np.int32, np.int32)):
+        pntrb, pntre, indx, val = random_csr(rng, m, n, 9, pt, it, hub=1700, gaps=True)
+        val = val.astype(vt)
+        x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+        sop = sop_for(name)
+        generic = msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
+        z0 = rng.uniform(-1, 1, size=(m, k)).astype(vt) if generic else np.zeros((m, k), vt)
+        want = z0.copy()
+        assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop,
+                          zero_first=not generic) == 0
+        st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0, k, sop=sop)
+        assert st == 0
+        info = api.call_info()
+        assert info.hub_rows >= 1 and info.kernel_launches >= 4
+        assert rel_err(z, want) <= RTOL[np.dtype(vt)], (name, k, it, pt)
+
+
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_wide_rows_and_every_tiling(cuda_device, oracle, vt):
+    rng = np.random.default_rng(11)
+    m, n = 300, 257
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 6, np.int64, np.int32, hub=900)
+    val = val.astype(vt)
+    w = 4 if vt == np.float32 else 2
+    tilings = [(4, 1), (8, 1), (8, 2), (8, 4), (16, 1), (16, 2), (16, 4), (32, 1), (32, 2), (32, 4), (32, 8)]
+    try:
+        for g, nv in tilings:
+            for k in (g * nv * w, g * nv * w - w):
+                if k <= 0:
+                    continue
+                x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+                for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_TDIST, M.SOP_FR), (M.MSG_SPMM, 0)):
+                    want = np.zeros((m, k), vt)
+                    oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop)
+                    assert api.set_option("force_tiling", (g << 8) | nv) == 0
+                    st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0,
+                                    np.zeros((m, k), vt), k, sop=sop)
+                    info = api.call_info()
+                    assert st == 0 and (info.lanes_per_edge, info.vectors_per_lane) == (g, nv)
+                    assert rel_err(z, want) <= RTOL[np.dtype(vt)], (g, nv, k, hex(msg))
+    finally:
+        api.set_option("force_tiling", 0)
+    # wider than any tiling: element-strided engine
+    k = 1024 * (4 // w) + 8 if vt == np.float32 else 600
+    x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+    want = np.zeros((m, k), vt)
+    oracle.csr(M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=1)
+    st, z = run_gpu(cuda_device, M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0,
+                    np.zeros((m, k), vt), k, sop=1)
+    assert st == 0 and rel_err(z, want) <= RTOL[np.dtype(vt)]
+
+
+def test_generic_kernel_equals_specialised_kernels(cuda_device):
+    rng = np.random.default_rng(5)
+    m, n, k = 800, 800, 128
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 12, np.int32, np.int32, hub=1200)
+    val = val.astype(np.float32)
+    x = np.nan_to_num(dense(rng, m, k, k, np.float32))
+    for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_TDIST, M.SOP_FR), (M.MSG_SPMM, 0), (M.MSG_GCN, 0)):
+        _, a = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, x, k, 0.0,
+                       np.zeros((m, k), np.float32), k, sop=sop)
+        api.set_option("force_generic", 1)
+        try:
+            _, b = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, x, k, 0.0,
+                           np.zeros((m, k), np.float32), k, sop=sop)
+            assert api.call_info().pattern == 0
+        finally:
+            api.set_option("force_generic", 0)
+        assert rel_err(a, b) <= 2e-6, hex(msg)  # same order of operations; only FMA contraction may differ
+
+
+def test_host_pointers_padding_and_beta(cuda_device, oracle):
+    """NumPy (host) arrays: staged in, Z copied back; ld > k padding is neither read nor written;
+    beta == 0 overwrites, beta != 0 accumulates (kernels/src/kernels.c:501-520)."""
+    rng = np.random.default_rng(21)
+    m, n, k, ld = 700, 650, 64, 72
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 8, np.int64, np.int64, hub=800)
+    val = val.astype(np.float32)
+    x, y = dense(rng, m, k, ld, np.float32), dense(rng, n, k, ld, np.float32)  # NaN in the padding
+    for beta in (0.0, 1.0):
+        z = np.full((m, ld), 3.0, np.float32)
+        want = z.copy()
+        oracle.csr(M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, np.nan_to_num(x), ld, np.nan_to_num(y), ld,
+                   beta, want, ld, sop_kind=1, zero_first=True)
+        st = api.fusedMM_csr(M.MSG_SIGMOID, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, ld, y, ld, beta,
+                             z, ld)
+        info = api.call_info()
+        assert st == 0 and info.h2d_bytes > 0 and info.d2h_bytes == m * k * 4
+        assert rel_err(z, want, k) <= 1e-4
+        assert (z[:, k:] == 3.0).all()
+    # the general kernel's behaviour (always accumulate) on request
+    api.set_option("beta_mode", 1)
+    try:
+        z = np.full((m, ld), 3.0, np.float32)
+        want = z.copy()
+        oracle.csr(M.MSG_GCN, m, n, k, val, indx, pntrb, pntre, np.nan_to_num(x), ld, np.nan_to_num(y), ld, 0.0,
+                   want, ld, zero_first=False)
+        assert api.fusedMM_csr(M.MSG_GCN, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, ld, y, ld, 0.0, z,
+                               ld) == 0
+        assert rel_err(z, want, k) <= 1e-4
+    finally:
+        api.set_option("beta_mode", 0)
+    # X aliasing Y on the host is staged once
+    z = np.zeros((m, ld), np.float32)
+    xx = dense(rng, max(m, n), k, ld, np.float32)
+    assert api.fusedMM_csr(M.MSG_TDIST, m, max(m, n), k, 1.0, 0, m, n, val, indx, pntrb, pntre, xx, ld, xx, ld,
+                           0.0, z, ld, sop=M.SOP_FR) == 0
+    want = np.zeros((m, ld), np.float32)
+    oracle.csr(M.MSG_TDIST, m, n, k, val, indx, pntrb, pntre, np.nan_to_num(xx), ld, np.nan_to_num(xx), ld, 0.0,
+               want, ld, sop_kind=M.SOP_FR)
+    assert rel_err(z, want, k) <= 1e-4
+
+
+def test_m_smaller_than_rows_and_unaligned_views(cuda_device, oracle):
+    import torch
+    rng = np.random.default_rng(8)
+    rows, n, k = 400, 300, 32
+    pntrb, pntre, indx, val = random_csr(rng, rows, n, 5, np.int32, np.int32)
+    val = val.astype(np.float32)
+    x, y = np.nan_to_num(dense(rng, rows, k, k, np.float32)), np.nan_to_num(dense(rng, n, k, k, np.float32))
+    # only rows [r0, r0+m) -- the way one shard of a row-partitioned matrix is computed
+    r0, m = 37, 123
+    want = np.zeros((rows, k), np.float32)
+    oracle.csr(M.MSG_SPMM, m, n, k, val, indx, pntrb[r0:], pntre[r0:], x[r0:], k, y, k, 0.0, want[r0:], k)
+    t = {nm: dev(a, cuda_device) for nm, a in dict(val=val, indx=indx, pb=pntrb, pe=pntre, x=x, y=y).items()}
+    z = torch.full((rows, k), 9.0, device=cuda_device)
+    st = api.fusedMM_csr(M.MSG_SPMM, m, n, k, 1.0, 0, rows, n, t["val"], t["indx"], t["pb"][r0:], t["pe"][r0:],
+                         t["x"][r0:], k, t["y"], k, 0.0, z[r0:], k)
+    assert st == 0
+    zc = z.cpu().numpy()
+    assert rel_err(zc[r0:r0 + m], want[r0:r0 + m]) <= 1e-4
+    assert (zc[:r0] == 9.0).all() and (zc[r0 + m:] == 9.0).all()
+    # a Y that starts 4 bytes off a 16-byte boundary cannot use 16-byte loads: element-strided engine
+    ybig = torch.zeros(n * k + 1, device=cuda_device)
+    yoff = ybig[1:].view(n, k)
+    yoff.copy_(t["y"])
+    z2 = torch.zeros((rows, k), device=cuda_device)
+    assert api.fusedMM_csr(M.MSG_SPMM, m, n, k, 1.0, 0, rows, n, t["val"], t["indx"], t["pb"][r0:], t["pe"][r0:],
+                           t["x"][r0:], k, yoff, k, 0.0, z2[r0:], k) == 0
+    assert api.call_info().lanes_per_edge == 0
+    assert rel_err(z2.cpu().numpy()[r0:r0 + m], want[r0:r0 + m]) <= 1e-4
+
+
+def test_caller_supplied_sop_udef_func_is_recognised(cuda_device, oracle):
+    """A host SOP_UDEF_FUNC (fusedMM.h:139) is matched against the device catalogue by sampling it."""
+    L = api.lib()
+    rng = np.random.default_rng(4)
+    m, n, k = 200, 200, 16
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 6, np.int64, np.int64)
+    val = val.astype(np.float32)
+    x = np.nan_to_num(dense(rng, m, k, k, np.float32))
+    HOOK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_float, ctypes.POINTER(ctypes.c_float))
+    fn = L.sfusedMM_csr_i64_udef
+    I, F, P = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
+    fn.argtypes = [ctypes.c_int32, I, I, I, F, I, I, I, P, P, P, P, P, I, P, I, F, P, I, HOOK]
+    fn.restype = ctypes.c_int
+
+    def call(body):
+        def hook(v, out):
+            out[0] = body(v)
+            return 0
+        z = np.zeros((m, k), np.float32)
+        st = fn(M.MSG_TDIST, m, n, k, 1.0, 0, m, n, val.ctypes.data, indx.ctypes.data, pntrb.ctypes.data,
+                pntre.ctypes.data, x.ctypes.data, k, x.ctypes.data, k, 0.0, z.ctypes.data, k, HOOK(hook))
+        return st, z, api.call_info().sop_kind
+
+    for body, kind, params in ((lambda v: 1.0 + 1.0 / v if v != 0 else np.inf, M.SOP_FR, (0, 0, 0)),
+                               (lambda v: 1.0 / (1.0 + v), M.SOP_TDIST, (0, 0, 0)),
+                               (lambda v: float(np.clip(-2.0 / (1.0 + v), -5, 5)) if v != -1 else -5.0,
+                                M.SOP_TDIST_CLAMPED, (0, 0, 0)),
+                               (lambda v: 3.0 / (2.0 + v) if v != -2 else np.inf, M.SOP_AFFINE_RECIP, (3.0, 2.0, 0.0))):
+        with np.errstate(all="ignore"):
+            st, z, got_kind = call(body)
+        assert st == 0 and got_kind == kind
+        want = np.zeros((m, k), np.float32)
+        oracle.csr(M.MSG_TDIST, m, n, k, val, indx, pntrb, pntre, x, k, x, k, 0.0, want, k, sop_kind=kind,
+                   sop_params=params)
+        assert rel_err(z, want) <= 1e-4
+    st, _, _ = call(lambda v: float(np.tanh(v)))  # not in the catalogue
+    assert st == M.ERR_UDEF
+
+
+def test_letter_dispatcher(cuda_device, oracle):
+    rng = np.random.default_rng(6)
+    m, n, k = 300, 300, 32
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 6, np.int32, np.int32)
+    for vt in (np.float32, np.float64):
+        x = np.nan_to_num(dense(rng, m, k, k, vt))
+        v = val.astype(vt)
+        for letter, msg in (("s", M.MSG_SIGMOID), ("t", M.MSG_TDIST), ("m", M.MSG_SPMM), ("g", M.MSG_GCN)):
+            api.set_sop(M.SOP_SIGMOID if letter == "s" else M.SOP_FR)
+            z = np.zeros((m, k), vt)
+            api.gfusedMM_csr(letter, m, n, k, 1.0, 0, m, n, v, indx, pntrb, pntre, x, k, x, k, 0.0, z, k)
+            want = np.zeros((m, k), vt)
+            oracle.csr(msg, m, n, k, v, indx, pntrb, pntre, x, k, x, k, 0.0, want, k,
+                       sop_kind=M.SOP_SIGMOID if letter == "s" else M.SOP_FR)
+            assert rel_err(z, want) <= RTOL[np.dtype(vt)], letter
+    api.set_sop(M.SOP_SIGMOID)
+
+
+def test_scratch_grows_when_there_are_many_split_rows(cuda_device, oracle):
+    """More split rows than the initial hub list holds: the chunk passes report the overflow, the host
+    enlarges the scratch and reruns them; whole rows are not recomputed."""
+    m, n, k, deg = 70000, 64, 4, 33
+    rng = np.random.default_rng(9)
+    pntrb = (np.arange(m) * deg).astype(np.int32)
+    pntre = pntrb + deg
+    indx = rng.integers(0, n, size=m * deg).astype(np.int32)
+    val = rng.uniform(0.5, 1.0, size=m * deg).astype(np.float32)
+    y = np.nan_to_num(dense(rng, n, k, k, np.float32))
+    api.set_option("hub_chunk", 32)
+    try:
+        z0 = np.ones((m, k), np.float32)
+        st, z = run_gpu(cuda_device, M.MSG_SPMM, m, n, k, val, indx, pntrb, pntre, None, k, y, k, 1.0, z0, k)
+        info = api.call_info()
+    finally:
+        api.set_option("hub_chunk", 512)
+    assert st == 0 and info.hub_rows == m and info.hub_chunks == 2 * m
+    want = np.ones((m, k), np.float32)
+    oracle.csr(M.MSG_SPMM, m, n, k, val, indx, pntrb, pntre, y, k, y, k, 1.0, want, k)
+    assert rel_err(z, want) <= 1e-4
+
+
+def test_async_stream_entry(cuda_device, oracle):
+    import torch
+    rng = np.random.default_rng(10)
+    m, n, k = 500, 500, 128
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 10, np.int64, np.int32, hub=700)
+    val = val.astype(np.float32)
+    x = np.nan_to_num(dense(rng, m, k, k, np.float32))
+    t = [dev(a, cuda_device) for a in (val, indx, pntrb, pntre, x)]
+    z = torch.zeros((m, k), device=cuda_device)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        st = api.fusedMM_csr(M.MSG_SIGMOID, m, n, k, 1.0, 0, m, n, t[0], t[1], t[2], t[3], t[4], k, t[4], k, 0.0,
+                             z, k, sop=M.SOP_SIGMOID, stream=s.cuda_stream)
+    assert st == 0
+    s.synchronize()
+    assert api.lib().fusedmm_b200_stream_status() == 0
+    want = np.zeros((m, k), np.float32)
+    oracle.csr(M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, x, k, x, k, 0.0, want, k, sop_kind=1)
+    assert rel_err(z.cpu().numpy(), want) <= 1e-4
+    # host arrays are refused on a caller's stream
+    assert api.fusedMM_csr(M.MSG_SIGMOID, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, k, x, k, 0.0,
+                           np.zeros((m, k), np.float32), k, stream=s.cuda_stream) == M.ERR_ARG
+
+
+@pytest.mark.parametrize("name", ["c1_sigmoid_rmat14_k128"])
+def test_benchmark_config_1_full_size(cuda_device, oracle, name):
+    """The configuration the reference can run on a CPU, at full size, float32 and float64."""
+    import torch
+    for dtype, vt in ((torch.float32, np.float32), (torch.float64, np.float64)):
+        cfg, csr, x = synth.make_config(name, device="cpu", dtype=dtype, ptr_dtype=torch.int64,
+                                        idx_dtype=torch.int32)
+        n, k = csr.n, cfg["k"]
+        rp, ix, vl, xs = csr.rowptr.numpy(), csr.indx.numpy(), csr.val.numpy(), x.numpy()
+        want = np.zeros((n, k), vt)
+        assert oracle.csr(cfg["msg"], n, n, k, vl, ix, rp[:-1].copy(), rp[1:].copy(), xs, k, xs, k, 0.0, want,
+                          k, sop_kind=cfg["sop"]) == 0
+        st, z = run_gpu(cuda_device, cfg["msg"], n, n, k, vl, ix, rp[:-1].copy(), rp[1:].copy(), xs, k, xs, k,
+                        0.0, np.zeros((n, k), vt), k, sop=cfg["sop"])
+        assert st == 0 and api.call_info().hub_rows > 0
+        assert rel_err(z, want) <= RTOL[np.dtype(vt)]
+
+
+def test_properties_at_benchmark_size(cuda_device):
+    """Size-independent checks on the headline workload (R-MAT scale 20, K=256) without a CPU pass:
+    GCN of an all-ones Y counts neighbours exactly; SpMM is linear in Y; a run is reproducible bit for
+    bit; computing row shards separately gives the same bits as one call."""
+    import torch
+    cfg, csr, x = synth.make_config("c2_fr_rmat20_k256", device=cuda_device)
+    n, k = csr.n, cfg["k"]
+    pb, pe = csr.pntrb.contiguous(), csr.pntre.contiguous()
+
+    def call(msg, y, z, sop=None, rows=(0, n)):
+        r0, r1 = rows
+        return api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb[r0:], pe[r0:],
+                               x[r0:], k, y, k, 0.0, z[r0:], k, sop=sop)
+
+    ones = torch.ones((n, k), device=cuda_device)
+    z = torch.empty((n, k), device=cuda_device)
+    assert call(M.MSG_GCN, ones, z) == 0
+    deg = csr.degrees().to(torch.float32)
+    assert torch.equal(z, deg[:, None].expand(n, k))
+    assert api.call_info().hub_rows > 0
+
+    y2 = synth.dense_uniform(n, k, -1.0, 1.0, 7, device=cuda_device)
+    za, zb, zc = (torch.empty((n, k), device=cuda_device) for _ in range(3))
+    assert call(M.MSG_SPMM, x, za) == 0 and call(M.MSG_SPMM, y2, zb) == 0
+    assert call(M.MSG_SPMM, 2.0 * x - 0.5 * y2, zc) == 0
+    lin = 2.0 * za - 0.5 * zb
+    scale = torch.maximum(lin.abs().amax(dim=1, keepdim=True), torch.tensor(1e-20, device=cuda_device))
+    assert float(((zc - lin).abs() / scale).max()) <= 1e-4
+
+    z1, z2 = torch.empty((n, k), device=cuda_device), torch.empty((n, k), device=cuda_device)
+    assert call(cfg["msg"], x, z1, sop=cfg["sop"]) == 0 and call(cfg["msg"], x, z2, sop=cfg["sop"]) == 0
+    assert torch.equal(z1, z2) and bool(torch.isfinite(z1).all())
+    bounds = api.shard_rows(pb.cpu().numpy(), pe.cpu().numpy(), 4)
+    z3 = torch.zeros((n, k), device=cuda_device)
+    for g in range(4):
+        assert call(cfg["msg"], x, z3, sop=cfg["sop"], rows=(int(bounds[g]), int(bounds[g + 1]))) == 0
+    assert torch.equal(z1, z3)
