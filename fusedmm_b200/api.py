@@ -32,7 +32,8 @@ class CallInfo(C.Structure):
     _fields_ = [("kernel_launches", C.c_int32), ("pattern", C.c_int32), ("lanes_per_edge", C.c_int32),
                 ("vectors_per_lane", C.c_int32), ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64),
                 ("hub_rows", C.c_int64), ("hub_chunks", C.c_int64), ("device_ms", C.c_float),
-                ("sop_kind", C.c_int32)]
+                ("sop_kind", C.c_int32), ("ms_scan", C.c_float), ("ms_rows", C.c_float),
+                ("ms_chunks", C.c_float), ("ms_fixup", C.c_float), ("engine", C.c_int32)]
 
 
 def lib() -> C.CDLL:

@@ -7,6 +7,7 @@
 // CUDA is unusable the call fails with FUSEDMM_B200_ERR_CUDA.
 #include "../../include/fusedmm_b200.h"
 #include "fusedmm_kernels.cuh"
+#include "fusedmm_stream.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -20,8 +21,10 @@ namespace fmm {
 
 // per-pattern launchers (inst_*.cu)
 #define FMM_DECLARE_LAUNCHER(PN)                                                                      \
-   bool launch_vec_##PN##_f32(int, int, const Params<float> &, long long, cudaStream_t);              \
-   bool launch_vec_##PN##_f64(int, int, const Params<double> &, long long, cudaStream_t);
+   bool launch_vec_##PN##_f32(int, int, int, int, const Params<float> &, long long, cudaStream_t);    \
+   bool launch_vec_##PN##_f64(int, int, int, int, const Params<double> &, long long, cudaStream_t);   \
+   bool launch_vec_##PN##_f32_stream(int, int, int, int, const Params<float> &, int, cudaStream_t);   \
+   bool launch_vec_##PN##_f64_stream(int, int, int, int, const Params<double> &, int, cudaStream_t);
 FMM_DECLARE_LAUNCHER(generic)
 FMM_DECLARE_LAUNCHER(sigmoid)
 FMM_DECLARE_LAUNCHER(tdist)
@@ -29,31 +32,55 @@ FMM_DECLARE_LAUNCHER(spmm)
 FMM_DECLARE_LAUNCHER(gcn)
 
 template <>
-bool launch_vec<float>(int pattern, int G, int NV, const Params<float> &p, long long grid, cudaStream_t s)
+bool launch_vec<float>(int pattern, int G, int NV, int U, int warps, const Params<float> &p, long long grid, cudaStream_t s)
 {
    switch (pattern) {
-      case PAT_SIGMOID: return launch_vec_sigmoid_f32(G, NV, p, grid, s);
-      case PAT_TDIST:   return launch_vec_tdist_f32(G, NV, p, grid, s);
-      case PAT_SPMM:    return launch_vec_spmm_f32(G, NV, p, grid, s);
-      case PAT_GCN:     return launch_vec_gcn_f32(G, NV, p, grid, s);
-      default:          return launch_vec_generic_f32(G, NV, p, grid, s);
+      case PAT_SIGMOID: return launch_vec_sigmoid_f32(G, NV, U, warps, p, grid, s);
+      case PAT_TDIST:   return launch_vec_tdist_f32(G, NV, U, warps, p, grid, s);
+      case PAT_SPMM:    return launch_vec_spmm_f32(G, NV, U, warps, p, grid, s);
+      case PAT_GCN:     return launch_vec_gcn_f32(G, NV, U, warps, p, grid, s);
+      default:          return launch_vec_generic_f32(G, NV, U, warps, p, grid, s);
    }
 }
 template <>
-bool launch_vec<double>(int pattern, int G, int NV, const Params<double> &p, long long grid, cudaStream_t s)
+bool launch_vec<double>(int pattern, int G, int NV, int U, int warps, const Params<double> &p, long long grid, cudaStream_t s)
 {
    switch (pattern) {
-      case PAT_SIGMOID: return launch_vec_sigmoid_f64(G, NV, p, grid, s);
-      case PAT_TDIST:   return launch_vec_tdist_f64(G, NV, p, grid, s);
-      case PAT_SPMM:    return launch_vec_spmm_f64(G, NV, p, grid, s);
-      case PAT_GCN:     return launch_vec_gcn_f64(G, NV, p, grid, s);
-      default:          return launch_vec_generic_f64(G, NV, p, grid, s);
+      case PAT_SIGMOID: return launch_vec_sigmoid_f64(G, NV, U, warps, p, grid, s);
+      case PAT_TDIST:   return launch_vec_tdist_f64(G, NV, U, warps, p, grid, s);
+      case PAT_SPMM:    return launch_vec_spmm_f64(G, NV, U, warps, p, grid, s);
+      case PAT_GCN:     return launch_vec_gcn_f64(G, NV, U, warps, p, grid, s);
+      default:          return launch_vec_generic_f64(G, NV, U, warps, p, grid, s);
    }
 }
 template <typename T>
-void launch_any(const Params<T> &p, long long grid, cudaStream_t s)
+bool launch_stream(int pattern, int G, int NV, int U, int warps, const Params<T> &p, int sm_count, cudaStream_t s);
+template <>
+bool launch_stream<float>(int pattern, int G, int NV, int U, int warps, const Params<float> &p, int sm_count, cudaStream_t s)
 {
-   fused_any_kernel<T><<<static_cast<unsigned int>(grid), WARPS_PER_CTA * 32, 0, s>>>(p);
+   switch (pattern) {
+      case PAT_SIGMOID: return launch_vec_sigmoid_f32_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_TDIST:   return launch_vec_tdist_f32_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_SPMM:    return launch_vec_spmm_f32_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_GCN:     return launch_vec_gcn_f32_stream(G, NV, U, warps, p, sm_count, s);
+      default:          return launch_vec_generic_f32_stream(G, NV, U, warps, p, sm_count, s);
+   }
+}
+template <>
+bool launch_stream<double>(int pattern, int G, int NV, int U, int warps, const Params<double> &p, int sm_count, cudaStream_t s)
+{
+   switch (pattern) {
+      case PAT_SIGMOID: return launch_vec_sigmoid_f64_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_TDIST:   return launch_vec_tdist_f64_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_SPMM:    return launch_vec_spmm_f64_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_GCN:     return launch_vec_gcn_f64_stream(G, NV, U, warps, p, sm_count, s);
+      default:          return launch_vec_generic_f64_stream(G, NV, U, warps, p, sm_count, s);
+   }
+}
+template <typename T>
+void launch_any(const Params<T> &p, int warps, long long grid, cudaStream_t s)
+{
+   fused_any_kernel<T><<<static_cast<unsigned int>(grid), warps * 32, 0, s>>>(p);
 }
 template <typename T>
 void launch_fixup(const Params<T> &p, long long grid, cudaStream_t s)
@@ -98,10 +125,15 @@ struct DeviceCtx {
    bool ready = false;
    cudaStream_t stream = nullptr;
    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+   cudaEvent_t evk[4] = {nullptr, nullptr, nullptr, nullptr};  // after scan / rows / chunks (fix-up ends at ev1)
    int sm_count = 148;
    DevBuf stage[7];  // val, indx, pntrb, pntre, x, y, z
    DevBuf counter, hub_row, hub_base, partials;
    long long hub_cap = 0;
+   DevBuf part, heads;       // edge-stream scheduler scratch
+   long long part_cap = 0;   // quanta the partition array has room for
+   int async_engine = 0;     // engine of the latest asynchronous call (1 whole rows, 2 edge stream)
+   long long async_quantum = 0;
    DevBuf table_f, table_d;
    // bookkeeping of the latest asynchronous call, for fusedmm_b200_stream_status
    bool async_pending = false;
@@ -110,7 +142,8 @@ struct DeviceCtx {
 };
 
 struct Options {
-   int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 512, force_tiling = 0, force_generic = 0;
+   int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 512, force_tiling = 0, force_generic = 0, warps_per_cta = 8,
+           engine = 0, edge_quantum = 256;
 };
 
 std::mutex g_mu;
@@ -159,6 +192,7 @@ int get_ctx(DeviceCtx **out)
       CK(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
       CK(cudaEventCreate(&c.ev0));
       CK(cudaEventCreate(&c.ev1));
+      for (auto &e : c.evk) CK(cudaEventCreate(&e));
       CK(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
       CKI(ensure_buf(c.counter, 256));
       c.ready = true;
@@ -317,21 +351,27 @@ bool is_device_pointer(const void *p)
    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
-void choose_tiling(long long nvec, int *G, int *NV)
+void choose_tiling(long long nvec, int *G, int *NV, int *U)
 {
-   if (nvec <= 4) { *G = 4; *NV = 1; }
-   else if (nvec <= 8) { *G = 8; *NV = 1; }
-   else if (nvec <= 16) { *G = 16; *NV = 1; }
-   else if (nvec <= 32) { *G = 32; *NV = 1; }
-   else if (nvec <= 64) { *G = 32; *NV = 2; }
-   else if (nvec <= 128) { *G = 32; *NV = 4; }
-   else if (nvec <= 256) { *G = 32; *NV = 8; }
-   else { *G = 0; *NV = 0; }
+   if (nvec <= 4) { *G = 4; *NV = 1; *U = 4; }
+   else if (nvec <= 8) { *G = 8; *NV = 1; *U = 8; }
+   else if (nvec <= 16) { *G = 16; *NV = 1; *U = 8; }
+   else if (nvec <= 32) { *G = 32; *NV = 1; *U = 8; }
+   else if (nvec <= 64) { *G = 32; *NV = 2; *U = 4; }
+   else if (nvec <= 128) { *G = 32; *NV = 4; *U = 2; }
+   else if (nvec <= 256) { *G = 32; *NV = 8; *U = 1; }
+   else { *G = 0; *NV = 0; *U = 0; }
+}
+// U of the default instantiation of a (G, NV) tiling
+int default_u(int G, int NV)
+{
+   if (G == 4) return 4;
+   return NV >= 8 ? 1 : 8 / NV;
 }
 
 struct HostArgs {
    int32_t imessage;
-   long long m, n, k;
+   long long m, n, k, nnz;
    const void *val, *indx, *pntrb, *pntre, *x, *y;
    void *z;
    long long ldx, ldy, ldz;
@@ -486,30 +526,88 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    bool vec_ok = (a.k % W == 0) && (zld % W == 0) && aligned16(p.z) &&
                  (!need_x || ((a.ldx % W == 0) && aligned16(p.x))) &&
                  (!need_y || ((a.ldy % W == 0) && aligned16(p.y)));
-   int G = 0, NV = 0;
+   int G = 0, NV = 0, U = 0;
+   const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
    if (vec_ok) {
-      if (g_opt.force_tiling) { G = static_cast<int>(g_opt.force_tiling >> 8); NV = static_cast<int>(g_opt.force_tiling & 0xFF); }
-      else choose_tiling(a.k / W, &G, &NV);
+      if (g_opt.force_tiling) {
+         G = static_cast<int>((g_opt.force_tiling >> 8) & 0xFF);
+         NV = static_cast<int>(g_opt.force_tiling & 0xFF);
+         U = static_cast<int>((g_opt.force_tiling >> 16) & 0xFF);
+         if (U == 0) U = default_u(G, NV);
+      } else choose_tiling(a.k / W, &G, &NV, &U);
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
 
-   // ---- hub-row scratch -------------------------------------------------------------------------------
+   int launches = 0;
+   float ms = 0.f, ms_k[4] = {0.f, 0.f, 0.f, 0.f};
+   long long nh = 0, nchunks = 0;
+   // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
+   // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
+   const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
+   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine != 1;
+   p.counter = static_cast<unsigned long long *>(c.counter.ptr);
+
+   if (use_stream) {
+      // ---- edge-stream scheduler: partition, main kernel, fix-up ------------------------------------
+      p.quantum = g_opt.edge_quantum;
+      if (c.part_cap == 0 || c.heads.bytes == 0) {
+         long long want = 1 << 16;
+         if (a.nnz > 0 && a.nnz < (1ll << 38)) {  // nnz is only a sizing hint (the reference never reads it)
+            size_t free_b = 0, total_b = 0;
+            CK(cudaMemGetInfo(&free_b, &total_b));
+            const long long hint = a.nnz / p.quantum + 2;
+            if (static_cast<double>(hint) * a.k * es < 0.25 * static_cast<double>(free_b)) want = std::max(want, hint);
+         }
+         c.part_cap = std::max(c.part_cap, want);
+      }
+      for (int attempt = 0; attempt < 3; attempt++) {
+         CKI(ensure_buf(c.part, (c.part_cap + 1) * sizeof(long long)));
+         CKI(ensure_buf(c.heads, static_cast<size_t>(c.part_cap) * a.k * es));
+         p.part = static_cast<long long *>(c.part.ptr);
+         p.heads = static_cast<T *>(c.heads.ptr);
+         p.part_cap = std::min<long long>(c.part_cap, static_cast<long long>(c.heads.bytes / (static_cast<size_t>(a.k) * es)));
+         if (!async) CK(cudaEventRecord(c.ev0, st));
+         stream_partition_kernel<T><<<c.sm_count * 8, 256, 0, st>>>(p);
+         if (!async) CK(cudaEventRecord(c.evk[0], st));
+         if (!launch_stream<T>(pattern, G, NV, U, warps, p, c.sm_count, st)) return FUSEDMM_B200_ERR_ARG;
+         if (!async) CK(cudaEventRecord(c.evk[1], st));
+         stream_fixup_kernel<T><<<c.sm_count * 4, WARPS_PER_CTA * 32, 0, st>>>(p);
+         launches += 3;
+         CK(cudaGetLastError());
+         if (async) {
+            c.async_pending = true;
+            c.async_engine = 2;
+            c.async_k = a.k;
+            c.async_elt = es;
+            break;
+         }
+         CK(cudaEventRecord(c.ev1, st));
+         unsigned long long nq = 0;
+         CK(cudaMemcpyAsync(&nq, static_cast<unsigned long long *>(c.counter.ptr) + 1, sizeof(nq), cudaMemcpyDeviceToHost, st));
+         CK(cudaStreamSynchronize(st));
+         float t = 0.f;
+         CK(cudaEventElapsedTime(&t, c.ev0, c.ev1)); ms += t;
+         CK(cudaEventElapsedTime(&t, c.ev0, c.evk[0])); ms_k[0] += t;
+         CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;
+         CK(cudaEventElapsedTime(&t, c.evk[1], c.ev1)); ms_k[3] += t;
+         nchunks = static_cast<long long>(nq);
+         if (nchunks <= p.part_cap) break;
+         if (attempt == 2) return FUSEDMM_B200_ERR_LIMIT;
+         c.part_cap = nchunks + nchunks / 16 + 64;  // nothing but zero rows was written; enlarge and rerun
+      }
+   } else {
+   // ---- row scheduler: whole rows, chunks of long rows, fix-up ----------------------------------------
    if (c.hub_cap == 0) {
       c.hub_cap = 1 << 16;
       CKI(ensure_buf(c.hub_row, c.hub_cap * sizeof(long long)));
       CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
    }
    if (c.partials.bytes == 0) CKI(ensure_buf(c.partials, static_cast<size_t>(64) << 20));
-
-   int launches = 0;
-   const long long row_grid = (a.m + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
+   const long long row_grid = (a.m + warps - 1) / warps;
    const long long hub_grid = static_cast<long long>(c.sm_count) * 8;
-   float ms = 0.f;
-   long long nh = 0, nchunks = 0;
 
    for (int attempt = 0; attempt < 3; attempt++) {
-      p.counter = static_cast<unsigned long long *>(c.counter.ptr);
       p.hub_row = static_cast<long long *>(c.hub_row.ptr);
       p.hub_base = static_cast<long long *>(c.hub_base.ptr);
       p.hub_cap = c.hub_cap;
@@ -521,23 +619,27 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       scan_hub_rows<<<static_cast<unsigned int>((a.m + 255) / 256), 256, 0, st>>>(
          p.pntrb, p.pntre, p.ptr64, p.m, p.chunk, p.counter, p.hub_row, p.hub_base, p.hub_cap);
       launches++;
+      if (!async) CK(cudaEventRecord(c.evk[0], st));
       if (attempt == 0) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
          p.mode = MODE_ROWS;
          if (vec_ok) {
-            if (!launch_vec<T>(pattern, G, NV, p, row_grid, st)) return FUSEDMM_B200_ERR_ARG;
+            if (!launch_vec<T>(pattern, G, NV, U, warps, p, row_grid, st)) return FUSEDMM_B200_ERR_ARG;
          } else {
-            launch_any<T>(p, row_grid, st);
+            launch_any<T>(p, warps, row_grid, st);
          }
          launches++;
       }
+      if (!async) CK(cudaEventRecord(c.evk[1], st));
       p.mode = MODE_HUB_CHUNKS;
-      if (vec_ok) launch_vec<T>(pattern, G, NV, p, hub_grid, st);
-      else launch_any<T>(p, hub_grid, st);
+      if (vec_ok) launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, st);
+      else launch_any<T>(p, WARPS_PER_CTA, hub_grid, st);
+      if (!async) CK(cudaEventRecord(c.evk[2], st));
       launch_fixup<T>(p, c.sm_count, st);
       launches += 2;
       CK(cudaGetLastError());
       if (async) {
          c.async_pending = true;
+         c.async_engine = 1;
          c.async_k = a.k;
          c.async_elt = es;
          break;
@@ -549,6 +651,10 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       float t = 0.f;
       CK(cudaEventElapsedTime(&t, c.ev0, c.ev1));
       ms += t;
+      CK(cudaEventElapsedTime(&t, c.ev0, c.evk[0])); ms_k[0] += t;
+      CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;
+      CK(cudaEventElapsedTime(&t, c.evk[1], c.evk[2])); ms_k[2] += t;
+      CK(cudaEventElapsedTime(&t, c.evk[2], c.ev1)); ms_k[3] += t;
       nh = static_cast<long long>(packed >> HUB_SHIFT);
       nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
       if (nh <= p.hub_cap && nchunks <= p.chunk_cap) break;
@@ -560,6 +666,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
       }
       if (nchunks > p.chunk_cap) CKI(ensure_buf(c.partials, static_cast<size_t>(nchunks + nchunks / 8 + 64) * a.k * es));
+   }
    }
 
    if (!on_dev[6]) {
@@ -573,16 +680,18 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    t_info.vectors_per_lane = vec_ok ? NV : 0;
    t_info.h2d_bytes = h2d;
    t_info.d2h_bytes = d2h;
+   t_info.engine = use_stream ? 2 : 1;
    t_info.hub_rows = nh;
    t_info.hub_chunks = nchunks;
    t_info.device_ms = ms;
+   t_info.ms_scan = ms_k[0]; t_info.ms_rows = ms_k[1]; t_info.ms_chunks = ms_k[2]; t_info.ms_fixup = ms_k[3];
    t_info.sop_kind = d.sop == OP_UDEF ? sopk.kind : -1;
    return 0;
 }
 
 // hook_kind: 0 none, 1 float hook, 2 double hook
 int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage, int64_t m, int64_t n,
-             int64_t k, const void *val, const void *indx, const void *pntrb, const void *pntre,
+             int64_t k, int64_t nnz, const void *val, const void *indx, const void *pntrb, const void *pntre,
              const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
              const fusedmm_b200_sop *sop, void *hook, void *stream)
 {
@@ -613,7 +722,7 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
    DeviceCtx *c = nullptr;
    st = get_ctx(&c);
    if (st) return st;
-   HostArgs a = {imessage, m, n, k, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits};
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits};
    return dtype == 0 ? run_typed<float>(*c, a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_typed<double>(*c, a, d, sopk, static_cast<cudaStream_t>(stream));
 }
@@ -662,7 +771,7 @@ int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t 
                      int64_t ldz, const fusedmm_b200_sop *sop, void *stream)
 {
    (void)alpha; (void)nnz; (void)rows; (void)cols;  // never read by the reference either (fusedMM.c:487-744)
-   return run_call(dtype, ptr_bits, idx_bits, imessage, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy,
+   return run_call(dtype, ptr_bits, idx_bits, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy,
                    beta, z, ldz, sop, nullptr, stream);
 }
 
@@ -673,7 +782,7 @@ int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t 
             VT *z, const IT ldz)                                                                      \
    {                                                                                                  \
       (void)alpha; (void)nnz; (void)rows; (void)cols;                                                 \
-      return run_call(DT, PB, IB, imessage, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta,   \
+      return run_call(DT, PB, IB, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy, beta,   \
                       z, ldz, nullptr, nullptr, nullptr);                                             \
    }
 FMM_DEFINE_CSR(sfusedMM_csr_i32, float, int32_t, 0, 32, 32)
@@ -689,7 +798,7 @@ FMM_DEFINE_CSR(fusedMM_csr, float, int64_t, 0, 64, 64)
             VT *z, const IT ldz, int (*sop_udef)(VT, VT *))                                           \
    {                                                                                                  \
       (void)alpha; (void)nnz; (void)rows; (void)cols;                                                 \
-      return run_call(DT, PB, IB, imessage, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta,   \
+      return run_call(DT, PB, IB, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy, beta,   \
                       z, ldz, nullptr, reinterpret_cast<void *>(sop_udef), nullptr);                  \
    }
 FMM_DEFINE_CSR_UDEF(sfusedMM_csr_i32_udef, float, int32_t, 0, 32, 32)
@@ -704,7 +813,7 @@ int sfusedMM_csr_p64i32(const int32_t imessage, const int64_t m, const int64_t n
                         const float beta, float *z, const int64_t ldz)
 {
    (void)alpha; (void)nnz; (void)rows; (void)cols;
-   return run_call(0, 64, 32, imessage, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz,
+   return run_call(0, 64, 32, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz,
                    nullptr, nullptr, nullptr);
 }
 int dfusedMM_csr_p64i32(const int32_t imessage, const int64_t m, const int64_t n, const int64_t k,
@@ -714,7 +823,7 @@ int dfusedMM_csr_p64i32(const int32_t imessage, const int64_t m, const int64_t n
                         const double beta, double *z, const int64_t ldz)
 {
    (void)alpha; (void)nnz; (void)rows; (void)cols;
-   return run_call(1, 64, 32, imessage, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz,
+   return run_call(1, 64, 32, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz,
                    nullptr, nullptr, nullptr);
 }
 
@@ -727,7 +836,7 @@ int dfusedMM_csr_p64i32(const int32_t imessage, const int64_t m, const int64_t n
       (void)alpha; (void)nnz; (void)rows; (void)cols;                                                 \
       const int32_t msg = letter_to_message(tkern);                                                   \
       if (msg < 0) { fprintf(stderr, "Kernel not implemented yet!!!\n"); return; }                    \
-      int st = run_call(DT, PB, IB, msg, m, n, k, val, indx, pntrb, pntre, A, lda, B, ldb, beta, C,   \
+      int st = run_call(DT, PB, IB, msg, m, n, k, nnz, val, indx, pntrb, pntre, A, lda, B, ldb, beta, C,   \
                         ldc, nullptr, nullptr, nullptr);                                              \
       if (st) fprintf(stderr, "fusedmm_b200: %s: %s\n", #NAME, fusedmm_b200_status_string(st));      \
    }
@@ -758,9 +867,19 @@ int fusedmm_b200_stream_status(void)
    int st = get_ctx(&c);
    if (st) return st;
    if (!c->async_pending) return 0;
-   unsigned long long packed = 0;
-   CK(cudaMemcpy(&packed, c->counter.ptr, sizeof(packed), cudaMemcpyDeviceToHost));
+   unsigned long long words[2] = {0, 0};
+   CK(cudaMemcpy(words, c->counter.ptr, sizeof(words), cudaMemcpyDeviceToHost));
    c->async_pending = false;
+   if (c->async_engine == 2) {
+      const long long nq = static_cast<long long>(words[1]);
+      const long long cap = std::min<long long>(c->part_cap, static_cast<long long>(c->heads.bytes / (static_cast<size_t>(c->async_k) * c->async_elt)));
+      if (nq <= cap) return 0;
+      c->part_cap = nq + nq / 16 + 64;
+      CKI(ensure_buf(c->part, (c->part_cap + 1) * sizeof(long long)));
+      CKI(ensure_buf(c->heads, static_cast<size_t>(c->part_cap) * c->async_k * c->async_elt));
+      return FUSEDMM_B200_ERR_LIMIT;
+   }
+   const unsigned long long packed = words[0];
    const long long nh = static_cast<long long>(packed >> HUB_SHIFT);
    const long long nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
    const long long cap = static_cast<long long>(c->partials.bytes / (static_cast<size_t>(c->async_k) * c->async_elt));
@@ -791,6 +910,9 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "hub_chunk")) return &g_opt.hub_chunk;
    if (!strcmp(name, "force_tiling")) return &g_opt.force_tiling;
    if (!strcmp(name, "force_generic")) return &g_opt.force_generic;
+   if (!strcmp(name, "warps_per_cta")) return &g_opt.warps_per_cta;
+   if (!strcmp(name, "engine")) return &g_opt.engine;
+   if (!strcmp(name, "edge_quantum")) return &g_opt.edge_quantum;
    return nullptr;
 }
 int fusedmm_b200_set_option(const char *name, int64_t value)
@@ -800,6 +922,9 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
    if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.engine && value > 2) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.edge_quantum && (value < 32 || value > (1ll << 24))) return FUSEDMM_B200_ERR_ARG;
    *s = value;
    return 0;
 }
@@ -849,9 +974,10 @@ int fusedmm_b200_release(void)
       cudaSetDevice(c.device);
       cudaStreamSynchronize(c.stream);
       DevBuf *bufs[] = {&c.stage[0], &c.stage[1], &c.stage[2], &c.stage[3], &c.stage[4], &c.stage[5], &c.stage[6],
-                        &c.hub_row, &c.hub_base, &c.partials, &c.table_f, &c.table_d};
+                        &c.hub_row, &c.hub_base, &c.partials, &c.table_f, &c.table_d, &c.part, &c.heads};
       for (DevBuf *b : bufs) { if (b->ptr) cudaFree(b->ptr); b->ptr = nullptr; b->bytes = 0; }
       c.hub_cap = 0;
+      c.part_cap = 0;
    }
    cudaSetDevice(cur);
    return 0;

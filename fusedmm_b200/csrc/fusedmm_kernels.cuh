@@ -67,6 +67,11 @@ struct Params {
    long long *hub_row, *hub_base;
    long long hub_cap, chunk_cap;
    T *partials;                  // chunk_cap x k
+   // edge-stream scheduler (fusedmm_stream.cuh): the edges are cut into quanta of `quantum` edges
+   long long quantum;            // edges per work item
+   long long *part;              // part[w] = row that holds the first edge of quantum w   (part_cap+1 entries)
+   long long part_cap;           // quanta the scratch has room for
+   T *heads;                     // heads[w] = partial sum of the row that straddles the start of quantum w
    // optional replication of the finished Z rows into other GPUs' Z buffers (multi-GPU all-gather
    // fused into the epilogue); z_peer[i] has the same layout as z
    int n_peers;
@@ -358,7 +363,7 @@ struct VecEngine {
    }
 };
 
-constexpr int WARPS_PER_CTA = 8;
+constexpr int WARPS_PER_CTA = 8;  // upper bound; the launch chooses blockDim.x = 32 * (1..8)
 
 // One warp per row (MODE_ROWS) or a grid-stride loop over the chunks of split rows
 // (MODE_HUB_CHUNKS).  Rows longer than p.chunk are skipped in MODE_ROWS.
@@ -370,8 +375,9 @@ fused_vec_kernel(const Params<T> p)
    constexpr int W = Eng::W;
    const int lane = threadIdx.x & 31;
    const int aop = pick<AOPC>(p.aop);
-   long long wid = static_cast<long long>(blockIdx.x) * WARPS_PER_CTA + (threadIdx.x >> 5);
-   const long long stride = static_cast<long long>(gridDim.x) * WARPS_PER_CTA;
+   const int wpc = blockDim.x >> 5;
+   long long wid = static_cast<long long>(blockIdx.x) * wpc + (threadIdx.x >> 5);
+   const long long stride = static_cast<long long>(gridDim.x) * wpc;
    long long nh = 0, nchunks = 0;
    if (p.mode == MODE_HUB_CHUNKS) {
       const unsigned long long c = *p.counter;
@@ -435,8 +441,9 @@ fused_any_kernel(const Params<T> p)
    const bool need_y = vop_reads_y(vop);
    const bool use_val = (rop == ROP_NOOP) && (vsc != VSC_NOOP);
    const bool use_sop_udef = (p.sop == OP_UDEF);
-   long long wid = static_cast<long long>(blockIdx.x) * WARPS_PER_CTA + (threadIdx.x >> 5);
-   const long long stride = static_cast<long long>(gridDim.x) * WARPS_PER_CTA;
+   const int wpc = blockDim.x >> 5;
+   long long wid = static_cast<long long>(blockIdx.x) * wpc + (threadIdx.x >> 5);
+   const long long stride = static_cast<long long>(gridDim.x) * wpc;
    long long nh = 0, nchunks = 0;
    if (p.mode == MODE_HUB_CHUNKS) {
       const unsigned long long c = *p.counter;
@@ -533,8 +540,9 @@ hub_fixup_kernel(const Params<T> p)
    const long long nh = static_cast<long long>(c >> HUB_SHIFT);
    const long long nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
    if (nh > p.hub_cap || nchunks > p.chunk_cap) return;
-   const long long stride = static_cast<long long>(gridDim.x) * WARPS_PER_CTA;
-   for (long long slot = static_cast<long long>(blockIdx.x) * WARPS_PER_CTA + (threadIdx.x >> 5); slot < nh;
+   const int wpc = blockDim.x >> 5;
+   const long long stride = static_cast<long long>(gridDim.x) * wpc;
+   for (long long slot = static_cast<long long>(blockIdx.x) * wpc + (threadIdx.x >> 5); slot < nh;
         slot += stride) {
       const long long row = p.hub_row[slot], base = p.hub_base[slot];
       const long long deg = ld_index(p.pntre, row, p.ptr64) - ld_index(p.pntrb, row, p.ptr64);
@@ -557,9 +565,9 @@ enum : int { PAT_GENERIC = 0, PAT_SIGMOID = 1, PAT_TDIST = 2, PAT_SPMM = 3, PAT_
 // Launches fused_vec_kernel<T, pattern ops, G, NV, U> with `grid` CTAs on `stream`.
 // Returns false when that (G, NV) tiling is not instantiated.
 template <typename T>
-bool launch_vec(int pattern, int G, int NV, const Params<T> &p, long long grid, cudaStream_t stream);
+bool launch_vec(int pattern, int G, int NV, int U, int warps, const Params<T> &p, long long grid, cudaStream_t stream);
 template <typename T>
-void launch_any(const Params<T> &p, long long grid, cudaStream_t stream);
+void launch_any(const Params<T> &p, int warps, long long grid, cudaStream_t stream);
 template <typename T>
 void launch_fixup(const Params<T> &p, long long grid, cudaStream_t stream);
 

@@ -1,0 +1,48 @@
+"""Multi-GPU row sharding: one process per GPU, rows cut into nnz-balanced contiguous shards, Y
+replicated, Z shards exchanged over NCCL (NVLink 5 / NVSwitch).
+
+The compute of a shard is an ordinary ``fusedMM_csr`` call on a row range (the four-array CSR needs no
+re-basing), so only the exchange lives here.  The shards are ragged (equal edges, not equal rows), so the
+exchange is one broadcast per owner, all in flight together; with the ``gloo`` backend the same code runs
+on CPU tensors, which is how the host logic is tested without GPUs.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import api
+
+
+def shard_bounds(rowptr_host: np.ndarray, world: int) -> np.ndarray:
+    """Row bounds of ``world`` shards with (nearly) equal edge counts; ``rowptr_host`` has m+1 entries."""
+    rp = np.ascontiguousarray(rowptr_host)
+    return api.shard_rows(rp[:-1].copy(), rp[1:].copy(), world)
+
+
+def exchange_row_shards(z, bounds, dist, group=None):
+    """Every rank owns rows [bounds[r], bounds[r+1]) of ``z`` (same shape on all ranks); afterwards every
+    rank holds all rows.  Enqueued on the current stream; returns when the work is enqueued (NCCL) or
+    done (gloo)."""
+    world = dist.get_world_size(group)
+    works = []
+    for g in range(world):
+        r0, r1 = int(bounds[g]), int(bounds[g + 1])
+        if r1 > r0:
+            works.append(dist.broadcast(z[r0:r1], src=dist.get_global_rank(group, g) if group else g,
+                                        group=group, async_op=True))
+    for w in works:
+        w.wait()
+
+
+def fusedMM_csr_sharded(imessage, n, k, val, indx, rowptr, x, y, z, bounds, dist, sop=None, stream=None,
+                        group=None):
+    """The multi-GPU step: this rank computes its row shard of ``z`` on its GPU and the shards are
+    exchanged.  ``rowptr``, ``indx``, ``val``, ``x`` (all rows) and ``y`` are this rank's device copies."""
+    rank = dist.get_rank(group)
+    r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+    st = 0
+    if r1 > r0:
+        st = api.fusedMM_csr(imessage, r1 - r0, n, k, 1.0, int(indx.numel()), n, n, val, indx, rowptr[r0:-1],
+                             rowptr[r0 + 1:], x[r0:], k, y, k, 0.0, z[r0:], k, sop=sop, stream=stream)
+    exchange_row_shards(z, bounds, dist, group)
+    return st

@@ -209,7 +209,12 @@ int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb
  *   "accept_vop_noop" 0 (default): VOP_NOOP returns status 2 as in the reference (fusedMM.c:346-377);
  *                    1: VOP_NOOP means T = Y_v.
  *   "hub_chunk"      edges per work item for rows that are split across warps (default 512).
- *   "force_tiling"   0 = automatic; otherwise (lanes_per_edge << 8) | vectors_per_lane.
+ *   "force_tiling"   0 = automatic; otherwise (gathers_in_flight << 16) | (lanes_per_edge << 8) |
+ *                    vectors_per_lane, gathers_in_flight 0 meaning that tiling's default.
+ *   "warps_per_cta"  1..8 (default 8): block size of the main kernel.
+ *   "engine"         0 (default): edge-stream scheduler whenever pntre == pntrb + 1 entry and the
+ *                    16-byte vector path applies, else the row scheduler; 1: always the row scheduler.
+ *   "edge_quantum"   edges per work item of the edge-stream scheduler (default 256).
  *   "force_generic"  1 = run every message through the flag-interpreting kernel.
  * fusedmm_b200_get_option(name, &value) reads them back.
  * ---------------------------------------------------------------------------------------------- */
@@ -224,10 +229,16 @@ typedef struct fusedmm_b200_call_info {
    int32_t vectors_per_lane;
    int64_t h2d_bytes;         /* staged host->device bytes                                   */
    int64_t d2h_bytes;         /* device->host bytes (Z)                                      */
-   int64_t hub_rows;          /* rows split across several warps                             */
-   int64_t hub_chunks;        /* partial-row work items                                      */
+   int64_t hub_rows;          /* row scheduler: rows split across several warps              */
+   int64_t hub_chunks;        /* row scheduler: partial-row work items; edge stream: quanta  */
    float   device_ms;         /* CUDA-event time of the kernels of a synchronous call        */
    int32_t sop_kind;          /* SOP that ran                                                */
+   /* CUDA-event time of each launch of a synchronous call, in launch order */
+   float   ms_scan;           /* scan_hub_rows: finds the rows to split                      */
+   float   ms_rows;           /* main kernel, one warp per whole row                         */
+   float   ms_chunks;         /* main kernel over the chunks of split rows                   */
+   float   ms_fixup;          /* hub_fixup_kernel: adds the chunk partials into Z            */
+   int32_t engine;            /* 1 = row scheduler, 2 = edge-stream scheduler                */
 } fusedmm_b200_call_info;
 int fusedmm_b200_last_call_info(fusedmm_b200_call_info *out);
 

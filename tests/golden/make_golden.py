@@ -36,8 +36,10 @@ def main():
                 ld = k + (case % 3)
                 pntrb, pntre, indx, val = random_csr(rng, m, n, 5, it, it, hub=70, gaps=(case % 2 == 1))
                 val = val.astype(vt)
-                x = dense(rng, m, k, ld, vt)
-                y = dense(rng, n, k, ld, vt)
+                generic = msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
+                lo, hi = (0.1, 1.0) if generic else (-0.5, 0.5)  # no cancelling reductions feeding a product
+                x = dense(rng, m, k, ld, vt, lo, hi)
+                y = dense(rng, n, k, ld, vt, lo, hi)
                 z = np.zeros((m, ld), dtype=vt)
                 sop = SOP_FOR.get(name, M.SOP_IDENTITY)
                 st = ref.csr(msg, m, n, k, val, indx, pntrb, pntre, np.nan_to_num(x), ld, np.nan_to_num(y), ld,

@@ -22,10 +22,21 @@ def dev(a, device):
     return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(device)
 
 
+def as_rowptr(pntrb, pntre):
+    """(pntrb, pntre) -> one rowptr array when row r+1 starts where row r ends, else None."""
+    if len(pntrb) and (pntre[:-1] == pntrb[1:]).all():
+        return np.concatenate([pntrb, pntre[-1:]])
+    return None
+
+
 def run_gpu(device, msg, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz, sop=None):
-    """device-resident call; returns (status, Z as numpy)."""
+    """device-resident call; returns (status, Z as numpy).  With pntre=None, pntrb is a rowptr array of
+    m+1 entries and the call gets the two views (rowptr, rowptr+1) of it, as callers of the reference
+    pass them; that is also what selects the edge-stream scheduler."""
     import torch
     t = [dev(a, device) for a in (val, indx, pntrb, pntre, x, y, z)]
+    if pntre is None:
+        t[2], t[3] = t[2][:-1], t[2][1:]
     st = api.fusedMM_csr(msg, m, n, k, 1.0, 0, m, n, t[0], t[1], t[2], t[3], t[4], ldx, t[5], ldy, beta,
                          t[6], ldz, sop=sop)
     torch.cuda.synchronize()
@@ -45,43 +56,61 @@ def test_golden_outputs_of_the_reference(cuda_device):
     data = np.load(GOLDEN)
     keys = sorted({k.split("_")[0] for k in data.files})
     assert len(keys) == 44
-    engines = set()
+    engines, schedulers = set(), set()
     for key in keys:
         msg, m, n, k, ld, sop = (int(v) for v in data[key + "_meta"])
         want = data[key + "_z"]
+        rowptr = as_rowptr(data[key + "_pntrb"], data[key + "_pntre"])
         st, z = run_gpu(cuda_device, msg, m, n, k, data[key + "_val"], data[key + "_indx"],
-                        data[key + "_pntrb"], data[key + "_pntre"], data[key + "_x"], ld, data[key + "_y"],
+                        data[key + "_pntrb"] if rowptr is None else rowptr,
+                        data[key + "_pntre"] if rowptr is None else None, data[key + "_x"], ld, data[key + "_y"],
                         ld, 0.0, np.zeros_like(want), ld, sop=sop)
         assert st == 0
         engines.add(api.call_info().lanes_per_edge)
+        schedulers.add(api.call_info().engine)
         assert rel_err(z, want, k) <= RTOL[want.dtype], (key, str(data[key + "_name"]))
         assert (z[:, k:] == 0).all()  # padding columns are not written
     assert 0 in engines and len(engines) > 1  # both the vector engine and the element-strided one ran
+    assert schedulers == {1, 2}               # and both the row and the edge-stream scheduler
 
 
+@pytest.mark.parametrize("scheduler", ["rows", "stream"])
 @pytest.mark.parametrize("vt", [np.float32, np.float64])
 @pytest.mark.parametrize("name", list(MESSAGES))
-def test_every_message_against_the_oracle(cuda_device, oracle, vt, name):
+def test_every_message_against_the_oracle(cuda_device, oracle, vt, name, scheduler):
+    """Every message, both schedulers: "rows" gets a CSR with unused slots between rows (pntre[i] <
+    pntrb[i+1]), which only the row scheduler can take; "stream" gets (rowptr, rowptr+1)."""
     msg = MESSAGES[name]
-    rng = np.random.default_rng(abs(hash((name, vt.__name__))) % 2**31)
+    rng = np.random.default_rng(sum(map(ord, name + vt.__name__ + scheduler)))
     m, n = 1500, 1100
+    generic = msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
+    lo, hi = (0.1, 1.0) if generic else (-0.5, 0.5)  # no cancelling reductions feeding a product
     for k, it, pt in ((4, np.int32, np.int32), (32, np.int64, np.int64), (64, np.int32, np.int64),
                       (96, np.int32, np.int32), (128, np.int64, np.int64), (200, np.int32, np.int32),
                       (256, np.int32, np.int64), (30, np.int32, np.int32)):
-        pntrb, pntre, indx, val = random_csr(rng, m, n, 9, pt, it, hub=1700, gaps=True)
+        pntrb, pntre, indx, val = random_csr(rng, m, n, 9, pt, it, hub=1700, gaps=(scheduler == "rows"))
         val = val.astype(vt)
-        x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+        x, y = np.nan_to_num(dense(rng, m, k, k, vt, lo, hi)), np.nan_to_num(dense(rng, n, k, k, vt, lo, hi))
         sop = sop_for(name)
-        generic = msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
         z0 = rng.uniform(-1, 1, size=(m, k)).astype(vt) if generic else np.zeros((m, k), vt)
         want = z0.copy()
         assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop,
                           zero_first=not generic) == 0
-        st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0, k, sop=sop)
+        if scheduler == "stream":
+            st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, as_rowptr(pntrb, pntre), None, x, k, y, k,
+                            0.0, z0, k, sop=sop)
+        else:
+            st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0, k, sop=sop)
         assert st == 0
         info = api.call_info()
-        assert info.hub_rows >= 1 and info.kernel_launches >= 4
-        assert rel_err(z, want) <= RTOL[np.dtype(vt)], (name, k, it, pt)
+        if scheduler == "rows":
+            assert info.engine == 1 and info.hub_rows >= 1 and info.kernel_launches >= 4
+        elif info.lanes_per_edge:
+            assert info.engine == 2 and info.kernel_launches == 3 and info.hub_chunks >= m * 9 * 0.7 / 256
+        # the table sigmoid is a step function of s (bins of 10/2048): a last-bit difference in s from
+        # the order of summation can move an edge to the neighbouring bin, a step of up to 2.5e-3
+        tol = 5e-3 if sop == M.SOP_SIGMOID_TABLE_C else RTOL[np.dtype(vt)]
+        assert rel_err(z, want) <= tol, (name, k, it, pt)
 
 
 @pytest.mark.parametrize("vt", [np.float32, np.float64])
@@ -102,11 +131,12 @@ def test_wide_rows_and_every_tiling(cuda_device, oracle, vt):
                     want = np.zeros((m, k), vt)
                     oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop)
                     assert api.set_option("force_tiling", (g << 8) | nv) == 0
-                    st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0,
-                                    np.zeros((m, k), vt), k, sop=sop)
-                    info = api.call_info()
-                    assert st == 0 and (info.lanes_per_edge, info.vectors_per_lane) == (g, nv)
-                    assert rel_err(z, want) <= RTOL[np.dtype(vt)], (g, nv, k, hex(msg))
+                    for rp, pe, eng in ((pntrb, pntre, 1), (as_rowptr(pntrb, pntre), None, 2)):
+                        st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, rp, pe, x, k, y, k, 0.0,
+                                        np.zeros((m, k), vt), k, sop=sop)
+                        info = api.call_info()
+                        assert st == 0 and (info.lanes_per_edge, info.vectors_per_lane, info.engine) == (g, nv, eng)
+                        assert rel_err(z, want) <= RTOL[np.dtype(vt)], (g, nv, k, hex(msg), eng)
     finally:
         api.set_option("force_tiling", 0)
     # wider than any tiling: element-strided engine
@@ -287,6 +317,18 @@ def test_scratch_grows_when_there_are_many_split_rows(cuda_device, oracle):
     assert st == 0 and info.hub_rows == m and info.hub_chunks == 2 * m
     want = np.ones((m, k), np.float32)
     oracle.csr(M.MSG_SPMM, m, n, k, val, indx, pntrb, pntre, y, k, y, k, 1.0, want, k)
+    assert rel_err(z, want) <= 1e-4
+    # the edge-stream scheduler: more quanta than its partition array holds at first
+    api.lib().fusedmm_b200_release()
+    api.set_option("edge_quantum", 32)
+    try:
+        st, z = run_gpu(cuda_device, M.MSG_SPMM, m, n, k, val, indx, as_rowptr(pntrb, pntre), None, None, k, y, k,
+                        1.0, np.ones((m, k), np.float32), k)
+        info = api.call_info()
+    finally:
+        api.set_option("edge_quantum", 256)
+    assert st == 0 and info.engine == 2 and info.hub_chunks == (m * deg + 31) // 32 > 65536
+    assert info.kernel_launches == 6  # one rerun
     assert rel_err(z, want) <= 1e-4
 
 
