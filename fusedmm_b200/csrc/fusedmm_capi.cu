@@ -23,8 +23,8 @@ namespace fmm {
 #define FMM_DECLARE_LAUNCHER(PN)                                                                      \
    bool launch_vec_##PN##_f32(int, int, int, int, const Params<float> &, long long, cudaStream_t);    \
    bool launch_vec_##PN##_f64(int, int, int, int, const Params<double> &, long long, cudaStream_t);   \
-   bool launch_vec_##PN##_f32_stream(int, int, int, int, const Params<float> &, int, cudaStream_t);   \
-   bool launch_vec_##PN##_f64_stream(int, int, int, int, const Params<double> &, int, cudaStream_t);
+   bool launch_vec_##PN##_f32_stream(int, int, int, const Params<float> &, int, cudaStream_t);        \
+   bool launch_vec_##PN##_f64_stream(int, int, int, const Params<double> &, int, cudaStream_t);
 FMM_DECLARE_LAUNCHER(generic)
 FMM_DECLARE_LAUNCHER(sigmoid)
 FMM_DECLARE_LAUNCHER(tdist)
@@ -54,27 +54,27 @@ bool launch_vec<double>(int pattern, int G, int NV, int U, int warps, const Para
    }
 }
 template <typename T>
-bool launch_stream(int pattern, int G, int NV, int U, int warps, const Params<T> &p, int sm_count, cudaStream_t s);
+bool launch_stream(int pattern, int G, int NV, int warps, const Params<T> &p, int sm_count, cudaStream_t s);
 template <>
-bool launch_stream<float>(int pattern, int G, int NV, int U, int warps, const Params<float> &p, int sm_count, cudaStream_t s)
+bool launch_stream<float>(int pattern, int G, int NV, int warps, const Params<float> &p, int sm_count, cudaStream_t s)
 {
    switch (pattern) {
-      case PAT_SIGMOID: return launch_vec_sigmoid_f32_stream(G, NV, U, warps, p, sm_count, s);
-      case PAT_TDIST:   return launch_vec_tdist_f32_stream(G, NV, U, warps, p, sm_count, s);
-      case PAT_SPMM:    return launch_vec_spmm_f32_stream(G, NV, U, warps, p, sm_count, s);
-      case PAT_GCN:     return launch_vec_gcn_f32_stream(G, NV, U, warps, p, sm_count, s);
-      default:          return launch_vec_generic_f32_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_SIGMOID: return launch_vec_sigmoid_f32_stream(G, NV, warps, p, sm_count, s);
+      case PAT_TDIST:   return launch_vec_tdist_f32_stream(G, NV, warps, p, sm_count, s);
+      case PAT_SPMM:    return launch_vec_spmm_f32_stream(G, NV, warps, p, sm_count, s);
+      case PAT_GCN:     return launch_vec_gcn_f32_stream(G, NV, warps, p, sm_count, s);
+      default:          return launch_vec_generic_f32_stream(G, NV, warps, p, sm_count, s);
    }
 }
 template <>
-bool launch_stream<double>(int pattern, int G, int NV, int U, int warps, const Params<double> &p, int sm_count, cudaStream_t s)
+bool launch_stream<double>(int pattern, int G, int NV, int warps, const Params<double> &p, int sm_count, cudaStream_t s)
 {
    switch (pattern) {
-      case PAT_SIGMOID: return launch_vec_sigmoid_f64_stream(G, NV, U, warps, p, sm_count, s);
-      case PAT_TDIST:   return launch_vec_tdist_f64_stream(G, NV, U, warps, p, sm_count, s);
-      case PAT_SPMM:    return launch_vec_spmm_f64_stream(G, NV, U, warps, p, sm_count, s);
-      case PAT_GCN:     return launch_vec_gcn_f64_stream(G, NV, U, warps, p, sm_count, s);
-      default:          return launch_vec_generic_f64_stream(G, NV, U, warps, p, sm_count, s);
+      case PAT_SIGMOID: return launch_vec_sigmoid_f64_stream(G, NV, warps, p, sm_count, s);
+      case PAT_TDIST:   return launch_vec_tdist_f64_stream(G, NV, warps, p, sm_count, s);
+      case PAT_SPMM:    return launch_vec_spmm_f64_stream(G, NV, warps, p, sm_count, s);
+      case PAT_GCN:     return launch_vec_gcn_f64_stream(G, NV, warps, p, sm_count, s);
+      default:          return launch_vec_generic_f64_stream(G, NV, warps, p, sm_count, s);
    }
 }
 template <typename T>
@@ -143,7 +143,7 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 512, force_tiling = 0, force_generic = 0, warps_per_cta = 8,
-           engine = 0, edge_quantum = 256;
+           engine = 0, edge_quantum = 256, stream_depth = 16;
 };
 
 std::mutex g_mu;
@@ -545,12 +545,15 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
    // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
    const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
-   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine != 1;
+   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2;
    p.counter = static_cast<unsigned long long *>(c.counter.ptr);
 
    if (use_stream) {
       // ---- edge-stream scheduler: partition, main kernel, fix-up ------------------------------------
-      p.quantum = g_opt.edge_quantum;
+      p.quantum = (g_opt.edge_quantum + 31) / 32 * 32;
+      int depth = std::min(G, 8);  // at least one segment; a power of two <= 32
+      while (depth * 2 <= std::min<int64_t>(g_opt.stream_depth, 32)) depth *= 2;
+      p.depth = depth;
       if (c.part_cap == 0 || c.heads.bytes == 0) {
          long long want = 1 << 16;
          if (a.nnz > 0 && a.nnz < (1ll << 38)) {  // nnz is only a sizing hint (the reference never reads it)
@@ -570,7 +573,9 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          if (!async) CK(cudaEventRecord(c.ev0, st));
          stream_partition_kernel<T><<<c.sm_count * 8, 256, 0, st>>>(p);
          if (!async) CK(cudaEventRecord(c.evk[0], st));
-         if (!launch_stream<T>(pattern, G, NV, U, warps, p, c.sm_count, st)) return FUSEDMM_B200_ERR_ARG;
+         int swarps = warps;  // the ring of every warp must fit into the shared memory of one SM
+         while (swarps > 1 && static_cast<size_t>(swarps) * p.depth * NV * 512 > (static_cast<size_t>(96) << 10)) swarps /= 2;
+         if (!launch_stream<T>(pattern, G, NV, swarps, p, c.sm_count, st)) return FUSEDMM_B200_ERR_ARG;
          if (!async) CK(cudaEventRecord(c.evk[1], st));
          stream_fixup_kernel<T><<<c.sm_count * 4, WARPS_PER_CTA * 32, 0, st>>>(p);
          launches += 3;
@@ -913,6 +918,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "warps_per_cta")) return &g_opt.warps_per_cta;
    if (!strcmp(name, "engine")) return &g_opt.engine;
    if (!strcmp(name, "edge_quantum")) return &g_opt.edge_quantum;
+   if (!strcmp(name, "stream_depth")) return &g_opt.stream_depth;
    return nullptr;
 }
 int fusedmm_b200_set_option(const char *name, int64_t value)
@@ -925,6 +931,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.engine && value > 2) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.edge_quantum && (value < 32 || value > (1ll << 24))) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.stream_depth && (value < 1 || value > 32)) return FUSEDMM_B200_ERR_ARG;
    *s = value;
    return 0;
 }

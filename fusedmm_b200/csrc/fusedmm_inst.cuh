@@ -1,4 +1,4 @@
-// fusedmm_inst.cuh -- stamps out the vector-engine kernels of ONE (value type, message pattern) pair.
+// fusedmm_inst.cuh -- stamps out the kernels of ONE (value type, message pattern) pair.
 // Each inst_*.cu includes this once, so the patterns compile in parallel.
 #pragma once
 #include "fusedmm_kernels.cuh"
@@ -6,15 +6,19 @@
 
 namespace fmm {
 
-// (lanes per edge G, 16-byte vectors per lane NV, gathers in flight per slot U).  G*NV*16 bytes is
-// the longest row a tiling covers.  The first line holds the defaults (a lane holds at most 8 gathered
-// vectors); the second line holds alternatives with another U that "force_tiling" can select.
+// Row scheduler: (lanes per edge G, 16-byte vectors per lane NV, gathers in flight per slot U).
+// G*NV*16 bytes is the longest row a tiling covers; a lane holds at most 8 gathered vectors.
 #define FMM_FOR_EACH_TILING(X) \
    X(4, 1, 4) X(8, 1, 8) X(8, 2, 4) X(8, 4, 2) X(16, 1, 8) X(16, 2, 4) X(16, 4, 2) \
    X(32, 1, 8) X(32, 2, 4) X(32, 4, 2) X(32, 8, 1) \
-   X(32, 1, 4) X(32, 1, 16) X(32, 2, 2) X(32, 2, 8) X(32, 4, 1) X(32, 4, 4) X(16, 1, 4) X(16, 2, 8) X(16, 4, 4) \
-   X(4, 2, 4) X(4, 2, 2) X(4, 4, 1) X(4, 4, 2) X(4, 4, 4) X(4, 8, 1) X(4, 8, 2) X(8, 4, 1) X(8, 4, 4) X(8, 8, 1) X(8, 8, 2) \
-   X(16, 4, 1) X(16, 8, 1) X(16, 8, 2) X(8, 2, 2) X(8, 2, 8) X(16, 2, 2)
+   X(32, 1, 16) X(32, 2, 8) X(32, 4, 4) X(32, 8, 2) X(16, 2, 8) X(16, 4, 4) X(16, 1, 16) X(8, 2, 8) X(8, 4, 4) X(8, 8, 2) \
+   X(16, 8, 2) X(4, 4, 4) X(4, 2, 4) X(16, 8, 1) X(8, 8, 1) X(4, 8, 1)
+
+// Edge-stream scheduler: (G, NV).  Fewer lanes per edge means more elements per lane: fewer shuffle
+// steps per reduction and more edges in flight per warp, at the price of registers.
+#define FMM_FOR_EACH_STREAM_TILING(X) \
+   X(4, 1) X(4, 2) X(4, 4) X(4, 8) X(8, 1) X(8, 2) X(8, 4) X(8, 8) X(16, 1) X(16, 2) X(16, 4) X(16, 8) \
+   X(32, 1) X(32, 2) X(32, 4) X(32, 8)
 
 #define FMM_TILING_CASE(G_, NV_, U_)                                                                 \
    case ((U_) << 16) | ((G_) << 8) | (NV_):                                                           \
@@ -23,24 +27,27 @@ namespace fmm {
       return true;
 
 // persistent launch of the edge-stream kernel: as many CTAs as fit on the device at once
-#define FMM_STREAM_CASE(G_, NV_, U_)                                                                 \
-   case ((U_) << 16) | ((G_) << 8) | (NV_): {                                                         \
-      auto kern = fused_stream_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_>;                   \
+#define FMM_STREAM_CASE(G_, NV_)                                                                     \
+   case ((G_) << 8) | (NV_): {                                                                        \
+      auto kern = fused_stream_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_>;                       \
+      const size_t smem = static_cast<size_t>(warps) * p.depth * (NV_) * 512;                         \
+      if (smem > 48 * 1024 &&                                                                         \
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                     \
+                               static_cast<int>(smem)) != cudaSuccess) return false;                  \
       int per_sm = 0;                                                                                 \
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, 0) != cudaSuccess  \
-          || per_sm < 1) per_sm = 1;                                                                  \
-      kern<<<static_cast<unsigned int>(sm_count * per_sm), warps * 32, 0, stream>>>(p);               \
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, smem)              \
+             != cudaSuccess || per_sm < 1) return false;                                              \
+      kern<<<static_cast<unsigned int>(sm_count * per_sm), warps * 32, smem, stream>>>(p);            \
       return true;                                                                                    \
    }
 
 #define FMM_DEFINE_PATTERN_LAUNCHER(FN, T, VOPC, ROPC, VSCC, AOPC)                                   \
-   bool FN##_stream(int G, int NV, int U, int warps, const Params<T> &p, int sm_count,                \
-                    cudaStream_t stream)                                                              \
+   bool FN##_stream(int G, int NV, int warps, const Params<T> &p, int sm_count, cudaStream_t stream)  \
    {                                                                                                  \
       using T_ = T;                                                                                   \
       constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
-      switch ((U << 16) | (G << 8) | NV) {                                                            \
-         FMM_FOR_EACH_TILING(FMM_STREAM_CASE)                                                         \
+      switch ((G << 8) | NV) {                                                                        \
+         FMM_FOR_EACH_STREAM_TILING(FMM_STREAM_CASE)                                                  \
          default: return false;                                                                       \
       }                                                                                               \
    }                                                                                                  \
@@ -48,7 +55,7 @@ namespace fmm {
    {                                                                                                  \
       using T_ = T;                                                                                   \
       constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
-      switch ((U << 16) | (G << 8) | NV) {                                                                      \
+      switch ((U << 16) | (G << 8) | NV) {                                                            \
          FMM_FOR_EACH_TILING(FMM_TILING_CASE)                                                         \
          default: return false;                                                                       \
       }                                                                                               \

@@ -68,7 +68,8 @@ struct Params {
    long long hub_cap, chunk_cap;
    T *partials;                  // chunk_cap x k
    // edge-stream scheduler (fusedmm_stream.cuh): the edges are cut into quanta of `quantum` edges
-   long long quantum;            // edges per work item
+   long long quantum;            // edges per work item (a multiple of 32)
+   int depth;                    // neighbour rows in flight per virtual warp (power of two <= lanes per edge)
    long long *part;              // part[w] = row that holds the first edge of quantum w   (part_cap+1 entries)
    long long part_cap;           // quanta the scratch has room for
    T *heads;                     // heads[w] = partial sum of the row that straddles the start of quantum w
@@ -273,6 +274,7 @@ struct VecEngine {
    static constexpr int W = VecOf<T>::W;
    static constexpr int S = 32 / G;  // edge slots per warp
    static_assert(S * U <= 32 && (32 % (S * U)) == 0, "S*U must divide 32");
+   static_assert(U <= G && (U & (U - 1)) == 0, "U must be a power of two no larger than G");
 
    __device__ __forceinline__ static void run(const Params<T> &p, const WorkItem &w, int lane,
                                               T (&acc)[NV][W])
@@ -296,6 +298,18 @@ struct VecEngine {
          if (need_x && inb[v]) ld_vec(p.x + w.row * p.ldx + e0, xv[v]);
       }
 
+      // Gather buffers, zeroed once: vectors past the end of the row (K < G*NV*W) are never loaded
+      // and must stay 0 for the reductions; a skipped gather (edge slot past the end of the row)
+      // leaves older values behind, which is harmless because its result is not accumulated.
+      T yv[U][NV][W];
+#pragma unroll
+      for (int u = 0; u < U; u++)
+#pragma unroll
+         for (int v = 0; v < NV; v++)
+#pragma unroll
+            for (int i = 0; i < W; i++) yv[u][v][i] = T(0);
+      const int u_mine = lg / (G / U);  // the edge of a group whose scalar this lane ends up holding
+
       for (long long base = w.eb; base < w.ee; base += 32) {
          const long long j = base + lane;
          const long long my_cid = (j < w.ee && need_y) ? ld_index(p.indx, j, p.idx64) : 0;
@@ -303,7 +317,7 @@ struct VecEngine {
          const int nb = (w.ee - base) < 32 ? static_cast<int>(w.ee - base) : 32;
 #pragma unroll 1
          for (int t = 0; t < nb; t += S * U) {
-            T yv[U][NV][W];
+            // ---- U gathers per slot in flight ------------------------------------------------------
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
@@ -313,37 +327,58 @@ struct VecEngine {
                                              : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e));
                const T *yrow = p.y + cid * p.ldy;
 #pragma unroll
-               for (int v = 0; v < NV; v++) {
-#pragma unroll
-                  for (int i = 0; i < W; i++) yv[u][v][i] = T(0);
+               for (int v = 0; v < NV; v++)
                   if (need_y && ok[u] && inb[v]) ld_vec_nc(yrow + static_cast<long long>(v * G + lg) * W, yv[u][v]);
-               }
             }
+            // ---- pass 1: T = VOP(x, y) in place, and this lane's share of each edge's reduction ----
+            T part[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
-               const int e = t + u * S + slot;
-               T tv[NV][W];
-               T s = T(0);
+               T ps[W];
+#pragma unroll
+               for (int i = 0; i < W; i++) ps[i] = T(0);
 #pragma unroll
                for (int v = 0; v < NV; v++)
 #pragma unroll
                   for (int i = 0; i < W; i++) {
-                     tv[v][i] = vop_apply(vop, xv[v][i], yv[u][v][i]);
-                     if (rop != ROP_NOOP) s += rop_term(rop, xv[v][i], tv[v][i]);
+                     yv[u][v][i] = vop_apply(vop, xv[v][i], yv[u][v][i]);
+                     if (rop != ROP_NOOP) ps[i] += rop_term(rop, xv[v][i], yv[u][v][i]);
                   }
-               if (rop != ROP_NOOP) {
+               part[u] = ps[0];
 #pragma unroll
-                  for (int off = G / 2; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
-               } else {
-                  s = __shfl_sync(FULL, my_val, e);
+               for (int i = 1; i < W; i++) part[u] += ps[i];
+            }
+            if (rop != ROP_NOOP) {
+               // Transposing reduction over the G lanes of the slot: each step halves the number of
+               // values a lane holds, so the U totals cost U-1 + log2(G/U) shuffles instead of
+               // U*log2(G); afterwards lanes u*(G/U).. hold the total of edge u.
+#pragma unroll
+               for (int half = U / 2, off = G / 2; half >= 1; half >>= 1, off >>= 1) {
+                  const bool upper = (lg & off) != 0;
+#pragma unroll
+                  for (int q = 0; q < half; q++) {
+                     const T keep = upper ? part[q + half] : part[q];
+                     const T send = upper ? part[q] : part[q + half];
+                     part[q] = keep + __shfl_xor_sync(FULL, send, off);
+                  }
                }
-               const T out = use_sop_udef ? sop_udef(s, p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : s;
+#pragma unroll
+               for (int off = G / (2 * U); off > 0; off >>= 1) part[0] += __shfl_xor_sync(FULL, part[0], off);
+            } else {
+               part[0] = __shfl_sync(FULL, my_val, t + u_mine * S + slot);  // a_uv of "my" edge
+            }
+            // ---- SOP once for the U edges of the group (lane group u evaluates edge u) --------------
+            const T out_mine = use_sop_udef ? sop_udef(part[0], p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : part[0];
+            // ---- pass 2: scale and accumulate --------------------------------------------------------
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+               const T out = __shfl_sync(FULL, out_mine, u * (G / U), G);
                if (ok[u]) {
 #pragma unroll
                   for (int v = 0; v < NV; v++)
 #pragma unroll
                      for (int i = 0; i < W; i++) {
-                        T tt = tv[v][i];
+                        T tt = yv[u][v][i];
                         if (vsc == VSC_MUL) tt = out * tt;
                         else if (vsc == VSC_ADD) tt = out + tt;
                         acc[v][i] = aop_apply(aop, acc[v][i], tt);

@@ -23,6 +23,38 @@ namespace fmm {
 
 constexpr long long POS_INF_LL = 0x7fffffffffffffffLL;
 
+// ---- cp.async (global -> shared, 16 bytes, cached in L2 only) and its per-thread group bookkeeping ----
+__device__ __forceinline__ void cp_async_16(unsigned smem_addr, const void *gptr)
+{
+   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most n of this thread's most recent groups are still in flight; n is rounded down to
+// one of the values that have a case here (waiting for more than asked is always correct)
+__device__ __forceinline__ void cp_async_wait_pending(unsigned n)
+{
+   if (n >= 28) asm volatile("cp.async.wait_group 28;" ::: "memory");
+   else if (n >= 24) asm volatile("cp.async.wait_group 24;" ::: "memory");
+   else if (n >= 16) asm volatile("cp.async.wait_group 16;" ::: "memory");
+   else if (n >= 12) asm volatile("cp.async.wait_group 12;" ::: "memory");
+   else if (n >= 8) asm volatile("cp.async.wait_group 8;" ::: "memory");
+   else if (n >= 4) asm volatile("cp.async.wait_group 4;" ::: "memory");
+   else asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+template <typename T>
+__device__ __forceinline__ void ld_shared_vec(unsigned smem_addr, T (&out)[VecOf<T>::W]);
+template <>
+__device__ __forceinline__ void ld_shared_vec<float>(unsigned smem_addr, float (&out)[4])
+{
+   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                : "=f"(out[0]), "=f"(out[1]), "=f"(out[2]), "=f"(out[3]) : "r"(smem_addr) : "memory");
+}
+template <>
+__device__ __forceinline__ void ld_shared_vec<double>(unsigned smem_addr, double (&out)[2])
+{
+   asm volatile("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(out[0]), "=d"(out[1]) : "r"(smem_addr) : "memory");
+}
+
 struct StreamShape {
    long long e0, e1, nq;  // first edge, one past the last edge, number of quanta
 };
@@ -79,13 +111,19 @@ __global__ void __launch_bounds__(256) stream_partition_kernel(const Params<T> p
    }
 }
 
-template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U>
+template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 fused_stream_kernel(const Params<T> p)
 {
    constexpr int W = VecOf<T>::W;
    constexpr int S = 32 / G;
-   static_assert(G % U == 0, "U must divide G");
+   extern __shared__ __align__(16) unsigned char fmm_smem[];
+   // ring of this warp: `depth` stages x NV vectors x 512 bytes (16 bytes per lane): for a given stage
+   // and vector the 32 lanes' slots are contiguous, so the shared-memory accesses are conflict-free
+   constexpr int B = G < 8 ? G : 8;                         // edges per segment
+   const unsigned depth = static_cast<unsigned>(p.depth);  // power of two, B <= depth <= 32
+   const unsigned ring = static_cast<unsigned>(__cvta_generic_to_shared(fmm_smem)) +
+                         (threadIdx.x >> 5) * depth * NV * 512u + (threadIdx.x & 31) * 16u;
    const int vop = pick<VOPC>(p.vop), rop = pick<ROPC>(p.rop), vsc = pick<VSCC>(p.vsc), aop = pick<AOPC>(p.aop);
    const int lane = threadIdx.x & 31, lg = lane % G, slot = lane / G;
    const unsigned vmask = (G == 32) ? FULL : (((1u << G) - 1u) << (slot * G));
@@ -170,76 +208,115 @@ fused_stream_kernel(const Params<T> p)
       };
 
       // ---- the edge walk -------------------------------------------------------------------------
-      // Gather buffers.  Zeroed once: vectors past the end of the row (K < G*NV*W) are never loaded and
-      // must stay 0 for the reductions; a skipped gather (edge slot past the end of the quantum) leaves
-      // an older row behind, which is harmless because its result is not accumulated.
-      T yv[U][NV][W];
+      // Neighbour rows travel global -> shared memory with cp.async (16 bytes per lane and vector,
+      // L2 only), `depth` edges ahead of the one being consumed.  Every lane copies exactly the bytes
+      // it later reads back, so completion is tracked per thread with cp.async groups: no barrier, no
+      // spin-wait, and the gathers in flight cost shared memory instead of registers.
+      //
+      // Edges are consumed in segments of up to B edges of one row, in two passes over the staged
+      // rows.  Pass 1 leaves every lane with its share of each edge's reduction; one transposing
+      // shuffle reduction (B-1 + log2(G/B) shuffles for B edges instead of B*log2(G)) hands the total
+      // of edge e to lanes e*G/B.., where SOP runs once for all B edges; pass 2 fetches each edge's
+      // scalar with one shuffle and accumulates.  The B edges of a pass are independent, which is what
+      // keeps the pipelines busy with the few warps the register budget allows.
+      const long long count = b - a;
+      T yv[NV][W];
 #pragma unroll
-      for (int u = 0; u < U; u++)
+      for (int v = 0; v < NV; v++)
 #pragma unroll
-         for (int v = 0; v < NV; v++)
+         for (int q = 0; q < W; q++) yv[v][q] = T(0);  // vectors past K are never copied and stay 0
+
+      auto issue_gather = [&](long long j) {  // edge j of this quantum into its ring stage; one group per edge
+         if (j < count && need_y) {
+            const long long cid = ld_index(p.indx, a + j, p.idx64);  // same address for the G lanes: one broadcast load
+            const T *yrow = p.y + cid * p.ldy;
+            const unsigned st = static_cast<unsigned>(j) & (depth - 1);
 #pragma unroll
-            for (int i = 0; i < W; i++) yv[u][v][i] = T(0);
-      long long pos = a;
-      while (__any_sync(FULL, pos < b)) {
-         const int nb = pos < b ? ((b - pos) < G ? static_cast<int>(b - pos) : G) : 0;
-         const long long j = pos + lg;
-         const long long my_cid = (lg < nb && need_y) ? ld_index(p.indx, j, p.idx64) : 0;
-         const T my_val = (use_val && lg < nb) ? __ldg(p.val + j) : T(0);
-#pragma unroll 1
-         for (int t = 0; t < G; t += U) {
-            if (!__any_sync(FULL, t < nb)) break;
+            for (int v = 0; v < NV; v++)
+               if (inb[v]) cp_async_16(ring + (st * NV + v) * 512u, yrow + eoff[v]);
+         }
+         cp_async_commit();
+      };
+      for (unsigned d = 0; d < depth; d++) issue_gather(d);
+
+      long long i = 0;
+      while (__any_sync(FULL, i < count)) {
+         int len = 0;
+         if (i < count) {
+            while (a + i >= re0) flush_advance();  // leave finished (and empty) rows behind
+            const long long in_row = re0 - (a + i), left = count - i;
+            len = static_cast<int>(in_row < left ? in_row : left);
+            len = len < B ? len : B;
+         }
+         cp_async_wait_pending(depth - B);  // the groups of edges i .. i+B-1 have landed
+         // ---- pass 1: per-lane shares of the reductions ------------------------------------------
+         T part[B];
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-               const int e = t + u;
-               const bool ok = e < nb;
-               const long long cid = p.idx64 ? (static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid >> 32), e, G)) << 32) |
-                                                  static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, G))
-                                             : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e, G));
-               const T *yrow = p.y + cid * p.ldy;
+         for (int e = 0; e < B; e++) part[e] = T(0);
+         if (rop != ROP_NOOP) {
 #pragma unroll
-               for (int v = 0; v < NV; v++)
-                  if (need_y && ok && inb[v]) ld_vec_nc(yrow + eoff[v], yv[u][v]);
-            }
+            for (int e = 0; e < B; e++) {
+               if (e < len) {
+                  const unsigned st = static_cast<unsigned>(i + e) & (depth - 1);
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-               const int e = t + u;
-               const bool ok = e < nb;
-               if (ok) {
-                  const long long eg = pos + e;
-                  while (eg >= re0) flush_advance();
-               }
-               T tv[NV][W];
-               T s = T(0);
-#pragma unroll
-               for (int v = 0; v < NV; v++)
-#pragma unroll
-                  for (int i = 0; i < W; i++) {
-                     tv[v][i] = vop_apply(vop, xv[v][i], yv[u][v][i]);
-                     if (rop != ROP_NOOP) s += rop_term(rop, xv[v][i], tv[v][i]);
-                  }
-               if (rop != ROP_NOOP) {
-#pragma unroll
-                  for (int off = G / 2; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
-               } else {
-                  s = __shfl_sync(FULL, my_val, e, G);
-               }
-               const T out = use_sop_udef ? sop_udef(s, p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : s;
-               if (ok) {
+                  for (int v = 0; v < NV; v++)
+                     if (need_y && inb[v]) ld_shared_vec(ring + (st * NV + v) * 512u, yv[v]);
+                  T ps = T(0);
 #pragma unroll
                   for (int v = 0; v < NV; v++)
 #pragma unroll
-                     for (int i = 0; i < W; i++) {
-                        T tt = tv[v][i];
-                        if (vsc == VSC_MUL) tt = out * tt;
-                        else if (vsc == VSC_ADD) tt = out + tt;
-                        acc[v][i] = aop_apply(aop, acc[v][i], tt);
-                     }
+                     for (int q = 0; q < W; q++) ps += rop_term(rop, xv[v][q], vop_apply(vop, xv[v][q], yv[v][q]));
+                  part[e] = ps;
                }
             }
+            // transposing reduction: after step k a lane keeps B >> (k+1) values
+#pragma unroll
+            for (int half = B / 2, off = G / 2; half >= 1; half >>= 1, off >>= 1) {
+               const bool upper = (lg & off) != 0;
+#pragma unroll
+               for (int t = 0; t < half; t++) {
+                  const T keep = upper ? part[t + half] : part[t];
+                  const T send = upper ? part[t] : part[t + half];
+                  part[t] = keep + __shfl_xor_sync(FULL, send, off);
+               }
+            }
+#pragma unroll
+            for (int off = G / (2 * B); off > 0; off >>= 1) part[0] += __shfl_xor_sync(FULL, part[0], off);
+         } else if (use_val) {
+            const int e_mine = lg / (G / B);  // this lane evaluates SOP for edge e_mine of the segment
+            if (e_mine < len) part[0] = __ldg(p.val + a + i + e_mine);
          }
-         pos += nb;
+         const T out_mine = use_sop_udef ? sop_udef(part[0], p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : part[0];
+         // ---- pass 2: scale and accumulate ----------------------------------------------------------
+#pragma unroll
+         for (int e = 0; e < B; e++) {
+            if (!__any_sync(FULL, e < len)) break;
+            const T out = __shfl_sync(FULL, out_mine, e * (G / B), G);
+            if (e < len) {
+               const unsigned st = static_cast<unsigned>(i + e) & (depth - 1);
+#pragma unroll
+               for (int v = 0; v < NV; v++)
+                  if (need_y && inb[v]) ld_shared_vec(ring + (st * NV + v) * 512u, yv[v]);
+#pragma unroll
+               for (int v = 0; v < NV; v++)
+#pragma unroll
+                  for (int q = 0; q < W; q++) {
+                     T tt = vop_apply(vop, xv[v][q], yv[v][q]);
+                     if (vsc == VSC_MUL) tt = out * tt;
+                     else if (vsc == VSC_ADD) tt = out + tt;
+                     acc[v][q] = aop_apply(aop, acc[v][q], tt);
+                  }
+            }
+         }
+         // ---- the stages of the segment are free again (their values were consumed above): refill ---
+#pragma unroll
+         for (int e = 0; e < B; e++)
+            if (e < len) issue_gather(i + depth + e);
+         i += len;
       }
+      cp_async_wait_pending(0);
+      const long long pos = a + count;
+      (void)pos;
       // ---- rows that end inside (a, b], then the row that continues past b -----------------------
       if (active) {
          while (r < p.m && re0 <= b) flush_advance();

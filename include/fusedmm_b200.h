@@ -212,9 +212,13 @@ int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb
  *   "force_tiling"   0 = automatic; otherwise (gathers_in_flight << 16) | (lanes_per_edge << 8) |
  *                    vectors_per_lane, gathers_in_flight 0 meaning that tiling's default.
  *   "warps_per_cta"  1..8 (default 8): block size of the main kernel.
- *   "engine"         0 (default): edge-stream scheduler whenever pntre == pntrb + 1 entry and the
- *                    16-byte vector path applies, else the row scheduler; 1: always the row scheduler.
- *   "edge_quantum"   edges per work item of the edge-stream scheduler (default 256).
+ *   "engine"         0 or 1 (default): the row scheduler (a warp per row, long rows cut into chunks);
+ *                    2: the edge-stream scheduler (equal-sized edge quanta, rows split where the
+ *                    quanta end) whenever pntre == pntrb + 1 entry and the 16-byte vector path applies.
+ *   "edge_quantum"   edges per work item of the edge-stream scheduler (default 256; rounded up to a
+ *                    multiple of 32).
+ *   "stream_depth"   neighbour rows each group of lanes keeps in flight in shared memory (default 16;
+ *                    rounded down to a power of two, at least 8 or the lanes per edge if fewer).
  *   "force_generic"  1 = run every message through the flag-interpreting kernel.
  * fusedmm_b200_get_option(name, &value) reads them back.
  * ---------------------------------------------------------------------------------------------- */
