@@ -270,7 +270,7 @@ def main():
     finite = bool(torch.isfinite(z[r0:r1]).all())
 
     # per-launch CUDA-event times of one synchronous call on this rank's shard
-    kms = {"scan": [], "rows": [], "chunks": [], "fixup": []}
+    kms = {"scan": [], "rows": [], "chunks": [], "fixup": [], "main": []}
     launches_per_step = 0
     for _ in range(5):
         st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all[r0:], pe_all[r0:], x[r0:],
@@ -283,10 +283,12 @@ def main():
     kmed = {nm: float(np.median(v)) for nm, v in kms.items()}
     peak, peak_kind = load_peaks()
     alg_bytes = synth.algorithmic_bytes(msg, my_edges, r1 - r0, k, es, 4, 8)
-    main_ms = kmed["rows"] + kmed["chunks"]
+    # the whole-row launch and the chunk launch of the main kernel run side by side on two streams, so the
+    # kernel time is the span that covers both (and the small fix-up launch that follows the chunks)
+    main_ms = kmed["main"]
     achieved = alg_bytes / (main_ms * 1e-3) * 1e-9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_kind": peak_kind, "kernel": "fused_vec_kernel (whole-row launch + split-row chunk launch)",
+                "traffic": None, "peak_kind": peak_kind, "kernel": "fused_vec_kernel: whole-row launch beside split-row chunk launch (+ fix-up), one span",
                 "algorithmic_bytes_per_step": alg_bytes, "kernel_ms": kmed,
                 "tiling": f"{info.lanes_per_edge} lanes/edge x {info.vectors_per_lane} vec/lane",
                 "split_rows": int(info.hub_rows), "row_chunks": int(info.hub_chunks)}

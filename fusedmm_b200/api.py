@@ -33,7 +33,7 @@ class CallInfo(C.Structure):
                 ("vectors_per_lane", C.c_int32), ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64),
                 ("hub_rows", C.c_int64), ("hub_chunks", C.c_int64), ("device_ms", C.c_float),
                 ("sop_kind", C.c_int32), ("ms_scan", C.c_float), ("ms_rows", C.c_float),
-                ("ms_chunks", C.c_float), ("ms_fixup", C.c_float), ("engine", C.c_int32)]
+                ("ms_chunks", C.c_float), ("ms_fixup", C.c_float), ("engine", C.c_int32), ("ms_main", C.c_float)]
 
 
 def lib() -> C.CDLL:

@@ -125,7 +125,9 @@ struct DeviceCtx {
    bool ready = false;
    cudaStream_t stream = nullptr;
    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-   cudaEvent_t evk[4] = {nullptr, nullptr, nullptr, nullptr};  // after scan / rows / chunks (fix-up ends at ev1)
+   cudaEvent_t evk[4] = {nullptr, nullptr, nullptr, nullptr};  // after scan / rows; start and end of the chunk launch
+   cudaStream_t side = nullptr;                 // the chunk and fix-up launches run beside the whole-row launch
+   cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_side_end = nullptr;
    int sm_count = 148;
    DevBuf stage[7];  // val, indx, pntrb, pntre, x, y, z
    DevBuf counter, hub_row, hub_base, partials;
@@ -142,7 +144,7 @@ struct DeviceCtx {
 };
 
 struct Options {
-   int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 512, force_tiling = 0, force_generic = 0, warps_per_cta = 8,
+   int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 512, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16;
 };
 
@@ -193,6 +195,10 @@ int get_ctx(DeviceCtx **out)
       CK(cudaEventCreate(&c.ev0));
       CK(cudaEventCreate(&c.ev1));
       for (auto &e : c.evk) CK(cudaEventCreate(&e));
+      CK(cudaStreamCreateWithFlags(&c.side, cudaStreamNonBlocking));
+      CK(cudaEventCreateWithFlags(&c.ev_fork, cudaEventDisableTiming));
+      CK(cudaEventCreateWithFlags(&c.ev_join, cudaEventDisableTiming));
+      CK(cudaEventCreate(&c.ev_side_end));
       CK(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
       CKI(ensure_buf(c.counter, 256));
       c.ready = true;
@@ -351,13 +357,15 @@ bool is_device_pointer(const void *p)
    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
-void choose_tiling(long long nvec, int *G, int *NV, int *U)
+// Default tiling for a row of `nvec` 16-byte vectors, from sweeps on B200 over the benchmark
+// configurations (K = 64 .. 512, float and double).
+void choose_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
 {
    if (nvec <= 4) { *G = 4; *NV = 1; *U = 4; }
    else if (nvec <= 8) { *G = 8; *NV = 1; *U = 8; }
-   else if (nvec <= 16) { *G = 16; *NV = 1; *U = 8; }
-   else if (nvec <= 32) { *G = 32; *NV = 1; *U = 8; }
-   else if (nvec <= 64) { *G = 32; *NV = 2; *U = 4; }
+   else if (nvec <= 16) { *G = 8; *NV = 2; *U = 4; }
+   else if (nvec <= 32) { *G = 16; *NV = 2; *U = 8; }
+   else if (nvec <= 64) { *G = 32; *NV = 2; *U = is_double ? 8 : 4; }
    else if (nvec <= 128) { *G = 32; *NV = 4; *U = 2; }
    else if (nvec <= 256) { *G = 32; *NV = 8; *U = 1; }
    else { *G = 0; *NV = 0; *U = 0; }
@@ -413,9 +421,17 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    bool on_dev[7];
    const bool used[7] = {need_val, need_y, true, true, need_x, need_y, true};
    for (int i = 0; i < 7; i++) on_dev[i] = used[i] ? is_device_pointer(dv[i]) : true;
-   if (async)
+   if (async) {
       for (int i = 0; i < 7; i++)
          if (!on_dev[i]) return FUSEDMM_B200_ERR_ARG;
+   } else {
+      // A synchronous call runs on the library's own stream.  Device arrays may still be the target of
+      // work the caller enqueued on other streams (a fill, a copy): wait for the device first, so that
+      // "synchronous" means what it means for the host function this replaces.
+      bool any_dev = false;
+      for (int i = 0; i < 7; i++) any_dev = any_dev || (used[i] && on_dev[i] && dv[i]);
+      if (any_dev) CK(cudaDeviceSynchronize());
+   }
 
    long long h2d = 0, d2h = 0;
    const bool pe_is_pb1 = (static_cast<const char *>(a.pntre) == static_cast<const char *>(a.pntrb) + ps);
@@ -534,13 +550,13 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          NV = static_cast<int>(g_opt.force_tiling & 0xFF);
          U = static_cast<int>((g_opt.force_tiling >> 16) & 0xFF);
          if (U == 0) U = default_u(G, NV);
-      } else choose_tiling(a.k / W, &G, &NV, &U);
+      } else choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
 
    int launches = 0;
-   float ms = 0.f, ms_k[4] = {0.f, 0.f, 0.f, 0.f};
+   float ms = 0.f, ms_k[4] = {0.f, 0.f, 0.f, 0.f}, ms_main = 0.f;
    long long nh = 0, nchunks = 0;
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
    // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
@@ -596,6 +612,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          CK(cudaEventElapsedTime(&t, c.ev0, c.evk[0])); ms_k[0] += t;
          CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;
          CK(cudaEventElapsedTime(&t, c.evk[1], c.ev1)); ms_k[3] += t;
+         CK(cudaEventElapsedTime(&t, c.evk[0], c.ev1)); ms_main += t;
          nchunks = static_cast<long long>(nq);
          if (nchunks <= p.part_cap) break;
          if (attempt == 2) return FUSEDMM_B200_ERR_LIMIT;
@@ -609,7 +626,8 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
    }
    if (c.partials.bytes == 0) CKI(ensure_buf(c.partials, static_cast<size_t>(64) << 20));
-   const long long row_grid = (a.m + warps - 1) / warps;
+   const long long rows_per_warp = vec_ok ? 32 / G : 1;  // short rows: one per group of G lanes
+   const long long row_grid = (a.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
    const long long hub_grid = static_cast<long long>(c.sm_count) * 8;
 
    for (int attempt = 0; attempt < 3; attempt++) {
@@ -625,6 +643,19 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          p.pntrb, p.pntre, p.ptr64, p.m, p.chunk, p.counter, p.hub_row, p.hub_base, p.hub_cap);
       launches++;
       if (!async) CK(cudaEventRecord(c.evk[0], st));
+      // The chunks of split rows (and their fix-up) and the whole rows are independent: they run on two
+      // streams, forked after the scan and joined before the call's stream continues.
+      CK(cudaEventRecord(c.ev_fork, st));
+      CK(cudaStreamWaitEvent(c.side, c.ev_fork, 0));
+      if (!async) CK(cudaEventRecord(c.evk[2], c.side));
+      p.mode = MODE_HUB_CHUNKS;
+      if (vec_ok) launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, c.side);
+      else launch_any<T>(p, WARPS_PER_CTA, hub_grid, c.side);
+      if (!async) CK(cudaEventRecord(c.evk[3], c.side));
+      launch_fixup<T>(p, c.sm_count, c.side);
+      if (!async) CK(cudaEventRecord(c.ev_side_end, c.side));
+      CK(cudaEventRecord(c.ev_join, c.side));
+      launches += 2;
       if (attempt == 0) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
          p.mode = MODE_ROWS;
          if (vec_ok) {
@@ -635,12 +666,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          launches++;
       }
       if (!async) CK(cudaEventRecord(c.evk[1], st));
-      p.mode = MODE_HUB_CHUNKS;
-      if (vec_ok) launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, st);
-      else launch_any<T>(p, WARPS_PER_CTA, hub_grid, st);
-      if (!async) CK(cudaEventRecord(c.evk[2], st));
-      launch_fixup<T>(p, c.sm_count, st);
-      launches += 2;
+      CK(cudaStreamWaitEvent(st, c.ev_join, 0));
       CK(cudaGetLastError());
       if (async) {
          c.async_pending = true;
@@ -658,8 +684,9 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       ms += t;
       CK(cudaEventElapsedTime(&t, c.ev0, c.evk[0])); ms_k[0] += t;
       CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;
-      CK(cudaEventElapsedTime(&t, c.evk[1], c.evk[2])); ms_k[2] += t;
-      CK(cudaEventElapsedTime(&t, c.evk[2], c.ev1)); ms_k[3] += t;
+      CK(cudaEventElapsedTime(&t, c.evk[2], c.evk[3])); ms_k[2] += t;
+      CK(cudaEventElapsedTime(&t, c.evk[3], c.ev_side_end)); ms_k[3] += t;
+      CK(cudaEventElapsedTime(&t, c.evk[0], c.ev1)); ms_main += t;
       nh = static_cast<long long>(packed >> HUB_SHIFT);
       nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
       if (nh <= p.hub_cap && nchunks <= p.chunk_cap) break;
@@ -690,6 +717,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    t_info.hub_chunks = nchunks;
    t_info.device_ms = ms;
    t_info.ms_scan = ms_k[0]; t_info.ms_rows = ms_k[1]; t_info.ms_chunks = ms_k[2]; t_info.ms_fixup = ms_k[3];
+   t_info.ms_main = ms_main;
    t_info.sop_kind = d.sop == OP_UDEF ? sopk.kind : -1;
    return 0;
 }

@@ -11,14 +11,11 @@ namespace fmm {
 #define FMM_FOR_EACH_TILING(X) \
    X(4, 1, 4) X(8, 1, 8) X(8, 2, 4) X(8, 4, 2) X(16, 1, 8) X(16, 2, 4) X(16, 4, 2) \
    X(32, 1, 8) X(32, 2, 4) X(32, 4, 2) X(32, 8, 1) \
-   X(32, 1, 16) X(32, 2, 8) X(32, 4, 4) X(32, 8, 2) X(16, 2, 8) X(16, 4, 4) X(16, 1, 16) X(8, 2, 8) X(8, 4, 4) X(8, 8, 2) \
-   X(16, 8, 2) X(4, 4, 4) X(4, 2, 4) X(16, 8, 1) X(8, 8, 1) X(4, 8, 1)
+   X(8, 2, 8) X(16, 2, 8) X(32, 2, 8) X(32, 4, 4)
 
-// Edge-stream scheduler: (G, NV).  Fewer lanes per edge means more elements per lane: fewer shuffle
-// steps per reduction and more edges in flight per warp, at the price of registers.
+// Edge-stream scheduler: (G, NV).
 #define FMM_FOR_EACH_STREAM_TILING(X) \
-   X(4, 1) X(4, 2) X(4, 4) X(4, 8) X(8, 1) X(8, 2) X(8, 4) X(8, 8) X(16, 1) X(16, 2) X(16, 4) X(16, 8) \
-   X(32, 1) X(32, 2) X(32, 4) X(32, 8)
+   X(4, 1) X(8, 1) X(8, 2) X(8, 4) X(16, 1) X(16, 2) X(16, 4) X(32, 1) X(32, 2) X(32, 4) X(32, 8)
 
 #define FMM_TILING_CASE(G_, NV_, U_)                                                                 \
    case ((U_) << 16) | ((G_) << 8) | (NV_):                                                           \

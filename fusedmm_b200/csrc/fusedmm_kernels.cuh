@@ -276,9 +276,17 @@ struct VecEngine {
    static_assert(S * U <= 32 && (32 % (S * U)) == 0, "S*U must divide 32");
    static_assert(U <= G && (U & (U - 1)) == 0, "U must be a power of two no larger than G");
 
+   // MULTI = false: the whole warp works on ONE item; its S slots take alternate edges and their
+   //                 accumulators are combined at the end (long rows and chunks of split rows).
+   // MULTI = true:  every slot has its OWN item (`w` differs between slots) and walks it alone: S short
+   //                 rows per warp, in lockstep, which is what keeps enough gathers in flight when the
+   //                 rows have only a handful of edges.
+   template <bool MULTI>
    __device__ __forceinline__ static void run(const Params<T> &p, const WorkItem &w, int lane,
                                               T (&acc)[NV][W])
    {
+      constexpr int BW = MULTI ? G : 32;  // column ids fetched per batch
+      constexpr int ES = MULTI ? 1 : S;   // distance between the edges u and u+1 of a slot
       const int vop = pick<VOPC>(p.vop), rop = pick<ROPC>(p.rop), vsc = pick<VSCC>(p.vsc),
                 aop = pick<AOPC>(p.aop);
       const int lg = lane % G, slot = lane / G;
@@ -309,22 +317,26 @@ struct VecEngine {
 #pragma unroll
             for (int i = 0; i < W; i++) yv[u][v][i] = T(0);
       const int u_mine = lg / (G / U);  // the edge of a group whose scalar this lane ends up holding
+      const int eslot = MULTI ? 0 : slot;
+      const int blane = MULTI ? lg : lane;
 
-      for (long long base = w.eb; base < w.ee; base += 32) {
-         const long long j = base + lane;
+      for (long long base = w.eb; MULTI ? __any_sync(FULL, base < w.ee) : (base < w.ee); base += BW) {
+         const long long j = base + blane;
          const long long my_cid = (j < w.ee && need_y) ? ld_index(p.indx, j, p.idx64) : 0;
          const T my_val = (use_val && j < w.ee) ? __ldg(p.val + j) : T(0);
-         const int nb = (w.ee - base) < 32 ? static_cast<int>(w.ee - base) : 32;
+         const long long left = w.ee - base;
+         const int nb = left < BW ? (left > 0 ? static_cast<int>(left) : 0) : BW;
 #pragma unroll 1
-         for (int t = 0; t < nb; t += S * U) {
+         for (int t = 0; MULTI ? __any_sync(FULL, t < nb) : (t < nb); t += ES * U) {
             // ---- U gathers per slot in flight ------------------------------------------------------
             bool ok[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
-               const int e = t + u * S + slot;  // < 32 because S*U divides 32
+               const int e = t + u * ES + eslot;  // < BW because ES*U divides BW
                ok[u] = e < nb;
-               const long long cid = p.idx64 ? shfl_ll(my_cid, e)
-                                             : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e));
+               const long long cid = p.idx64 ? (static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid >> 32), e, BW)) << 32) |
+                                                  static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW))
+                                             : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW));
                const T *yrow = p.y + cid * p.ldy;
 #pragma unroll
                for (int v = 0; v < NV; v++)
@@ -365,7 +377,7 @@ struct VecEngine {
 #pragma unroll
                for (int off = G / (2 * U); off > 0; off >>= 1) part[0] += __shfl_xor_sync(FULL, part[0], off);
             } else {
-               part[0] = __shfl_sync(FULL, my_val, t + u_mine * S + slot);  // a_uv of "my" edge
+               part[0] = __shfl_sync(FULL, my_val, t + u_mine * ES + eslot, BW);  // a_uv of "my" edge
             }
             // ---- SOP once for the U edges of the group (lane group u evaluates edge u) --------------
             const T out_mine = use_sop_udef ? sop_udef(part[0], p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : part[0];
@@ -389,7 +401,7 @@ struct VecEngine {
       }
       // combine the edge slots: afterwards every slot holds the row's result
 #pragma unroll
-      for (int off = G; off < 32; off <<= 1)
+      for (int off = G; !MULTI && off < 32; off <<= 1)
 #pragma unroll
          for (int v = 0; v < NV; v++)
 #pragma unroll
@@ -420,6 +432,44 @@ fused_vec_kernel(const Params<T> p)
       nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
       if (nh > p.hub_cap || nchunks > p.chunk_cap) return;  // scratch too small: the host enlarges it and reruns
    }
+   constexpr int S = 32 / G;
+   if (S > 1 && p.mode == MODE_ROWS) {
+      // short rows: every slot of the warp takes its own row
+      const int lg = lane % G, slot = lane / G;
+      if (wid * S >= p.m) return;
+      WorkItem w;
+      w.row = wid * S + slot;
+      w.dst_item = -1;
+      w.eb = w.ee = 0;
+      bool mine = w.row < p.m;
+      if (mine) {
+         w.eb = ld_index(p.pntrb, w.row, p.ptr64);
+         w.ee = ld_index(p.pntre, w.row, p.ptr64);
+         if (w.ee - w.eb > p.chunk) { mine = false; w.ee = w.eb; }  // split rows belong to the chunk launch
+      } else {
+         w.row = 0;
+      }
+      T acc[NV][W];
+      Eng::template run<true>(p, w, lane, acc);
+      if (mine) {
+         T *dst = p.z + w.row * p.ldz;
+#pragma unroll
+         for (int v = 0; v < NV; v++) {
+            const long long e0 = static_cast<long long>(v * G + lg) * W;
+            if (e0 < p.k) {
+               if (p.accumulate) {
+                  T old[W];
+                  ld_vec(dst + e0, old);
+#pragma unroll
+                  for (int i = 0; i < W; i++) acc[v][i] = aop_apply(aop, old[i], acc[v][i]);
+               }
+               st_vec(dst + e0, acc[v]);
+               for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
+            }
+         }
+      }
+      return;
+   }
    for (;; wid += stride) {
       WorkItem w;
       if (p.mode == MODE_ROWS) {
@@ -434,7 +484,7 @@ fused_vec_kernel(const Params<T> p)
          chunk_item(p, wid, nh, w);
       }
       T acc[NV][W];
-      Eng::run(p, w, lane, acc);
+      Eng::template run<false>(p, w, lane, acc);
 
       if (lane < G) {  // slot 0 holds (like every slot) the finished sums
          const bool to_z = w.dst_item < 0;

@@ -14,7 +14,8 @@
  * independently be a device pointer (used in place, nothing is copied) or a host pointer (staged to the
  * GPU for the call; Z is copied back before the call returns).  Residency is detected per pointer
  * with cudaPointerGetAttributes.  Unless stated otherwise a call is synchronous: Z is complete when
- * it returns, exactly like the reference.
+ * it returns, exactly like the reference; when it is given device arrays it first waits for all work
+ * already enqueued on the device (cudaDeviceSynchronize), because it runs on a stream of its own.
  *
  * There is no CPU implementation in this library.  If no CUDA device is usable every entry point
  * returns FUSEDMM_B200_ERR_CUDA.
@@ -211,7 +212,7 @@ int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb
  *   "hub_chunk"      edges per work item for rows that are split across warps (default 512).
  *   "force_tiling"   0 = automatic; otherwise (gathers_in_flight << 16) | (lanes_per_edge << 8) |
  *                    vectors_per_lane, gathers_in_flight 0 meaning that tiling's default.
- *   "warps_per_cta"  1..8 (default 8): block size of the main kernel.
+ *   "warps_per_cta"  1..8 (default 1): block size of the main kernel, in warps.
  *   "engine"         0 or 1 (default): the row scheduler (a warp per row, long rows cut into chunks);
  *                    2: the edge-stream scheduler (equal-sized edge quanta, rows split where the
  *                    quanta end) whenever pntre == pntrb + 1 entry and the 16-byte vector path applies.
@@ -243,6 +244,8 @@ typedef struct fusedmm_b200_call_info {
    float   ms_chunks;         /* main kernel over the chunks of split rows                   */
    float   ms_fixup;          /* hub_fixup_kernel: adds the chunk partials into Z            */
    int32_t engine;            /* 1 = row scheduler, 2 = edge-stream scheduler                */
+   float   ms_main;           /* from the end of the scan to the end of the last main-kernel /
+                                 fix-up launch (the whole-row and the chunk launches overlap)  */
 } fusedmm_b200_call_info;
 int fusedmm_b200_last_call_info(fusedmm_b200_call_info *out);
 

@@ -36,6 +36,9 @@ def random_csr(rng, m, n, avg_deg, ptr_dtype=np.int64, idx_dtype=np.int64, hub=N
         pos += int(degs[i]) + int(pad[i])
     total = max(pos, 1)
     indx = rng.integers(0, n, size=total).astype(idx_dtype)
+    for i in range(m):  # no self-loops: with X = Y they give a zero distance, and 1/0 in the FR / t-dist SOPs
+        seg = indx[starts[i]:starts[i] + degs[i]]
+        seg[seg == i] = (i + 1) % n
     val = rng.uniform(0.25, 1.5, size=total)
     pntrb = starts.astype(ptr_dtype)
     pntre = (starts + degs).astype(ptr_dtype)
