@@ -209,6 +209,8 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # NCCL's version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=dev)
     api.lib()
 
@@ -224,13 +226,31 @@ def main():
 
     from fusedmm_b200 import dist as fdist
     stream = torch.cuda.current_stream()
+    # N > 1: the Z exchange is fused into the kernels (stores into the peers' Z over NVLink) when torch's
+    # symmetric memory is available on this box, otherwise one NCCL broadcast per row shard follows the kernels
+    pz, exchange = None, None
+    if world > 1:
+        exchange = "nccl broadcast per row shard after the kernels"
+        if os.environ.get("FUSEDMM_BENCH_EXCHANGE", "fused") == "fused":
+            try:
+                pz = fdist.PeerZ(n, k, tdtype, dev, dist)
+                z = pz.z
+                z.zero_()
+                exchange = "fused: kernels store finished rows into every rank's Z (peer memory), one small all-reduce orders the ranks"
+            except Exception as exc:  # no symmetric memory on this box: keep the NCCL path
+                pz = None
+                exchange += f" (symmetric memory unavailable: {type(exc).__name__})"
+        config["exchange"] = exchange
+    peers = pz.peers_at_row(r0) if pz is not None else None
 
     def step():
         st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all[r0:], pe_all[r0:],
                              x[r0:], k, x, k, 0.0, z[r0:], k, sop=sop if sop is not None else 0,
-                             stream=stream.cuda_stream)
+                             stream=stream.cuda_stream, z_peers=peers)
         assert st == 0, api.status_string(st)
-        if world > 1:
+        if pz is not None:
+            pz.finish_step()
+        elif world > 1:
             fdist.exchange_row_shards(z, bounds, dist)
 
     def barrier():
@@ -267,7 +287,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / args.steps
     value = flops_per_edge * nnz / (ms_step * 1e-3) * 1e-9
-    finite = bool(torch.isfinite(z[r0:r1]).all())
+    finite = bool(torch.isfinite(z).all())
+    if world > 1:  # every rank must hold the same, complete Z: compare a checksum of checksums
+        chk = z.double().sum(dim=1).sum().reshape(1)
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        finite = finite and bool(lo.item() == hi.item())
 
     # per-launch CUDA-event times of one synchronous call on this rank's shard
     kms = {"scan": [], "rows": [], "chunks": [], "fixup": [], "main": []}

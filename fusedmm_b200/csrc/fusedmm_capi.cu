@@ -385,6 +385,8 @@ struct HostArgs {
    long long ldx, ldy, ldz;
    double beta;
    int ptr_bits, idx_bits;
+   int n_peers;
+   void *const *z_peers;
 };
 
 // extent (one past the largest edge position) of indx/val when they have to be staged
@@ -526,6 +528,16 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    p.accumulate = accumulate;
    p.chunk = std::max<int64_t>(32, g_opt.hub_chunk);
    p.n_peers = 0;
+   if (a.n_peers > 0) {
+      // finished rows are also stored into the peers' Z buffers (same layout as z): only meaningful for
+      // device-resident Z, and only the row scheduler's kernels carry the extra stores
+      if (!on_dev[6] || a.n_peers > 8 || !a.z_peers) return FUSEDMM_B200_ERR_ARG;
+      p.n_peers = a.n_peers;
+      for (int i = 0; i < a.n_peers; i++) {
+         if (!a.z_peers[i]) return FUSEDMM_B200_ERR_ARG;
+         p.z_peer[i] = static_cast<T *>(a.z_peers[i]);
+      }
+   }
    if (d.sop == OP_UDEF && sopk.kind == FUSEDMM_SOP_SIGMOID_TABLE_C) {
       DevBuf &tb = sizeof(T) == 4 ? c.table_f : c.table_d;
       if (!tb.ptr) {
@@ -542,6 +554,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    bool vec_ok = (a.k % W == 0) && (zld % W == 0) && aligned16(p.z) &&
                  (!need_x || ((a.ldx % W == 0) && aligned16(p.x))) &&
                  (!need_y || ((a.ldy % W == 0) && aligned16(p.y)));
+   for (int i = 0; i < p.n_peers; i++) vec_ok = vec_ok && aligned16(p.z_peer[i]);
    int G = 0, NV = 0, U = 0;
    const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
    if (vec_ok) {
@@ -561,7 +574,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
    // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
    const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
-   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2;
+   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2 && p.n_peers == 0;
    p.counter = static_cast<unsigned long long *>(c.counter.ptr);
 
    if (use_stream) {
@@ -726,7 +739,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
 int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage, int64_t m, int64_t n,
              int64_t k, int64_t nnz, const void *val, const void *indx, const void *pntrb, const void *pntre,
              const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
-             const fusedmm_b200_sop *sop, void *hook, void *stream)
+             const fusedmm_b200_sop *sop, void *hook, void *stream, int n_peers = 0, void *const *z_peers = nullptr)
 {
    std::lock_guard<std::mutex> lock(g_mu);
    memset(&t_info, 0, sizeof(t_info));
@@ -755,7 +768,7 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
    DeviceCtx *c = nullptr;
    st = get_ctx(&c);
    if (st) return st;
-   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits};
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, n_peers, z_peers};
    return dtype == 0 ? run_typed<float>(*c, a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_typed<double>(*c, a, d, sopk, static_cast<cudaStream_t>(stream));
 }
@@ -806,6 +819,19 @@ int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t 
    (void)alpha; (void)nnz; (void)rows; (void)cols;  // never read by the reference either (fusedMM.c:487-744)
    return run_call(dtype, ptr_bits, idx_bits, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy,
                    beta, z, ldz, sop, nullptr, stream);
+}
+
+int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage, int64_t m,
+                           int64_t n, int64_t k, double alpha, int64_t nnz, int64_t rows, int64_t cols,
+                           const void *val, const void *indx, const void *pntrb, const void *pntre,
+                           const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z,
+                           int64_t ldz, const fusedmm_b200_sop *sop, void *stream, int32_t n_peers,
+                           void *const *z_peers)
+{
+   (void)alpha; (void)rows; (void)cols;
+   if (n_peers < 0) return FUSEDMM_B200_ERR_ARG;
+   return run_call(dtype, ptr_bits, idx_bits, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy,
+                   beta, z, ldz, sop, nullptr, stream, n_peers, z_peers);
 }
 
 #define FMM_DEFINE_CSR(NAME, VT, IT, DT, PB, IB)                                                      \

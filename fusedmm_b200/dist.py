@@ -46,3 +46,46 @@ def fusedMM_csr_sharded(imessage, n, k, val, indx, rowptr, x, y, z, bounds, dist
                              rowptr[r0 + 1:], x[r0:], k, y, k, 0.0, z[r0:], k, sop=sop, stream=stream)
     exchange_row_shards(z, bounds, dist, group)
     return st
+
+
+class PeerZ:
+    """A Z matrix that every rank of the group can write into on every other rank (torch symmetric memory:
+    one allocation per GPU, peer-mapped over NVLink).  With it the exchange of the Z row shards is fused into
+    the compute kernels: ``fusedmm_b200_csr_multi`` stores each finished row into the local Z and into the
+    peers' Z, and a step ends with one small collective that orders the ranks."""
+
+    def __init__(self, n, k, dtype, device, dist, group=None):
+        import torch
+        import torch.distributed._symmetric_memory as symm_mem
+        self.dist, self.group = dist, group
+        self.z = symm_mem.empty((n, k), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.z, group if group is not None else dist.group.WORLD)
+        self.rank, self.world = self.handle.rank, self.handle.world_size
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert self.ptrs[self.rank] == self.z.data_ptr()
+        self.row_bytes = k * self.z.element_size()
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def peers_at_row(self, r0):
+        """Addresses of row ``r0`` in the other ranks' copies of Z."""
+        return [p + r0 * self.row_bytes for i, p in enumerate(self.ptrs) if i != self.rank]
+
+    def finish_step(self):
+        """Enqueue the collective that follows this rank's kernels in stream order; when it completes on a
+        rank, every rank's kernels of the step (and with them their stores into this rank's Z) are done."""
+        self.dist.all_reduce(self._token, group=self.group)
+
+
+def fusedMM_csr_fused_exchange(imessage, n, k, val, indx, rowptr, x, y, pz: PeerZ, bounds, sop=None,
+                               stream=None):
+    """The multi-GPU step with the exchange fused into the kernels: this rank computes its row shard and
+    the kernels write the finished rows into every rank's Z (``pz``).  ``stream`` must be the stream the
+    following collective is enqueued on (torch's current stream)."""
+    r0, r1 = int(bounds[pz.rank]), int(bounds[pz.rank + 1])
+    st = 0
+    if r1 > r0:
+        st = api.fusedMM_csr(imessage, r1 - r0, n, k, 1.0, int(indx.numel()), n, n, val, indx, rowptr[r0:-1],
+                             rowptr[r0 + 1:], x[r0:], k, y, k, 0.0, pz.z[r0:], k, sop=sop, stream=stream,
+                             z_peers=pz.peers_at_row(r0))
+    pz.finish_step()
+    return st

@@ -179,6 +179,23 @@ int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t 
                      const void *pntre, const void *x, int64_t ldx, const void *y, int64_t ldy,
                      double beta, void *z, int64_t ldz, const fusedmm_b200_sop *sop, void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * fusedmm_b200_csr with the Z exchange of a multi-GPU run fused into the kernels: every finished row
+ * of Z is stored into `z` and, with the same layout (same ldz, same row numbering), into each of the
+ * n_peers (<= 8) buffers z_peers[i], which are device addresses of OTHER GPUs' Z buffers that this
+ * GPU can write (peer-mapped memory, e.g. the buffer_ptrs of a torch symmetric-memory tensor, offset
+ * to this call's first row).  The stores are plain global stores that cross NVLink; nothing is read
+ * from a peer.  The caller orders the ranks: a peer's rows are complete in this GPU's Z once that peer's
+ * call has finished (stream order on the peer) and a cross-rank barrier or collective has been passed.
+ * No counterpart in the reference (which is single-process, fusedMM.c:487-744).
+ * ---------------------------------------------------------------------------------------------- */
+int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage,
+                           int64_t m, int64_t n, int64_t k, double alpha, int64_t nnz, int64_t rows,
+                           int64_t cols, const void *val, const void *indx, const void *pntrb,
+                           const void *pntre, const void *x, int64_t ldx, const void *y, int64_t ldy,
+                           double beta, void *z, int64_t ldz, const fusedmm_b200_sop *sop, void *stream,
+                           int32_t n_peers, void *const *z_peers);
+
 /* After work enqueued with a non-NULL stream has completed: 0, or FUSEDMM_B200_ERR_LIMIT when the
  * hub-row scratch was too small for that call (the scratch has then been enlarged; run the call again). */
 int fusedmm_b200_stream_status(void);

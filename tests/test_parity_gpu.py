@@ -341,6 +341,32 @@ def test_scratch_grows_when_there_are_many_split_rows(cuda_device, oracle):
     assert rel_err(z, want) <= 1e-4
 
 
+def test_peer_stores_replicate_finished_rows(cuda_device, oracle):
+    """fusedmm_b200_csr_multi: finished rows also go to the peers' Z buffers.  Two more buffers on the same
+    GPU stand in for the peers (on several GPUs the addresses come from peer-mapped memory); vector engine
+    with split rows, and the element-strided engine."""
+    import torch
+    rng = np.random.default_rng(31)
+    m, n = 900, 700
+    for k in (64, 30):
+        pntrb, pntre, indx, val = random_csr(rng, m, n, 7, np.int64, np.int32, hub=1300)
+        val = val.astype(np.float32)
+        x, y = np.nan_to_num(dense(rng, m, k, k, np.float32)), np.nan_to_num(dense(rng, n, k, k, np.float32))
+        r0 = 100  # a row shard: rows [r0, m)
+        t = [dev(a, cuda_device) for a in (val, indx, pntrb, pntre, x, y)]
+        zs = [torch.full((m, k), 5.0, device=cuda_device) for _ in range(3)]
+        st = api.fusedMM_csr(M.MSG_TDIST, m - r0, n, k, 1.0, 0, m, n, t[0], t[1], t[2][r0:], t[3][r0:], t[4][r0:],
+                             k, t[5], k, 0.0, zs[0][r0:], k, sop=M.SOP_TDIST,
+                             z_peers=[zs[1][r0:].data_ptr(), zs[2][r0:].data_ptr()])
+        torch.cuda.synchronize()
+        assert st == 0 and api.call_info().hub_rows >= 1
+        want = np.full((m, k), 5.0, np.float32)
+        oracle.csr(M.MSG_TDIST, m - r0, n, k, val, indx, pntrb[r0:].copy(), pntre[r0:].copy(), x[r0:], k, y, k, 0.0,
+                   want[r0:], k, sop_kind=M.SOP_TDIST)
+        assert rel_err(zs[0].cpu().numpy(), want) <= 1e-4
+        assert torch.equal(zs[0], zs[1]) and torch.equal(zs[0], zs[2])
+
+
 def test_async_stream_entry(cuda_device, oracle):
     import torch
     rng = np.random.default_rng(10)
