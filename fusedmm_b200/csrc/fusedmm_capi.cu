@@ -773,6 +773,183 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
                      : run_typed<double>(*c, a, d, sopk, static_cast<cudaStream_t>(stream));
 }
 
+// =====================================================================================================
+// The entry point that allocates nothing (fusedmm_b200_csr_static_scratch).
+//
+// Its split-row scratch (the hub list, the per-chunk partial sums, the packed counter, the sigmoid table)
+// is this file-scope device array instead of buffers obtained from cudaMalloc.  Every GPU on which the
+// library runs holds its own copy of the array from the moment the library is loaded until the process
+// exits.  In host code the name below is only a stand-in for the symbol, NOT a device address: the address
+// comes from cudaGetSymbolAddress, once per device, with that device current (static_scratch_base), and only
+// that address is ever handed to a kernel.
+// =====================================================================================================
+#define FUSEDMM_B200_STATIC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[FUSEDMM_B200_STATIC_SCRATCH_BYTES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+constexpr long long STATIC_HUB_CAP = 32768;                    // split rows the hub list has room for
+constexpr size_t STATIC_OFF_TABLE = 256;                       // after the packed counter
+constexpr size_t STATIC_OFF_HUB_ROW = STATIC_OFF_TABLE + SM_TABLE_SIZE * sizeof(double);
+constexpr size_t STATIC_OFF_HUB_BASE = STATIC_OFF_HUB_ROW + STATIC_HUB_CAP * sizeof(long long);
+constexpr size_t STATIC_OFF_PARTIALS = STATIC_OFF_HUB_BASE + STATIC_HUB_CAP * sizeof(long long);
+static_assert(STATIC_OFF_PARTIALS % 256 == 0, "the partial sums must start on a 256-byte boundary");
+
+struct StaticScratchSlot {
+   unsigned char *base = nullptr;  // device address of g_static_scratch on this device
+   int sm_count = 0;
+};
+StaticScratchSlot g_static_slot[STATIC_MAX_DEVICES];
+
+// Set-up, once per device, with that device current: ask the runtime where this device keeps the array.
+int static_scratch_base(StaticScratchSlot **out)
+{
+   int dev = 0;
+   CK(cudaGetDevice(&dev));
+   if (dev < 0 || dev >= STATIC_MAX_DEVICES) return FUSEDMM_B200_ERR_LIMIT;
+   StaticScratchSlot &slot = g_static_slot[dev];
+   if (!slot.base) {
+      void *ptr = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e != cudaSuccess || !ptr) {
+         fprintf(stderr, "fusedmm_b200: cudaGetSymbolAddress(static scratch) failed on device %d: %s\n", dev,
+                 cudaGetErrorString(e));
+         cudaGetLastError();
+         return FUSEDMM_B200_ERR_CUDA;
+      }
+      CK(cudaDeviceGetAttribute(&slot.sm_count, cudaDevAttrMultiProcessorCount, dev));
+      slot.base = static_cast<unsigned char *>(ptr);
+   }
+   *out = &slot;
+   return 0;
+}
+
+template <typename T>
+const T *static_host_sigmoid_table()
+{
+   static T table[SM_TABLE_SIZE];
+   static bool ready = false;
+   if (!ready) {
+      for (int i = 0; i < SM_TABLE_SIZE; i++) {
+         T x = static_cast<T>(2.0 * 5.0 * i / SM_TABLE_SIZE - 5.0);
+         table[i] = static_cast<T>(1.0 / (1 + std::exp(-static_cast<double>(x))));
+      }
+      ready = true;
+   }
+   return table;
+}
+
+// The row scheduler's four launches on ONE stream (no side stream, no events: creating them allocates),
+// with every scratch pointer inside the static array.
+template <typename T>
+int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_sop &sopk, cudaStream_t user_stream)
+{
+   constexpr int W = VecOf<T>::W;
+   const size_t es = sizeof(T), ps = a.ptr_bits / 8;
+   (void)ps;
+   const bool need_x = vop_reads_x(d.vop) || rop_reads_x(d.rop);
+   const bool need_y = vop_reads_y(d.vop);
+   const bool need_val = d.rop == ROP_NOOP && d.vsc != VSC_NOOP;
+   if ((need_x && !a.x) || (need_y && (!a.y || !a.indx)) || (need_val && !a.val) || !a.z || !a.pntrb || !a.pntre)
+      return FUSEDMM_B200_ERR_ARG;
+   if (a.ldz < a.k || (need_x && a.ldx < a.k) || (need_y && a.ldy < a.k)) return FUSEDMM_B200_ERR_ARG;
+   const void *arrays[7] = {a.val, a.indx, a.pntrb, a.pntre, a.x, a.y, a.z};
+   const bool used[7] = {need_val, need_y, true, true, need_x, need_y, true};
+   for (int i = 0; i < 7; i++)
+      if (used[i] && !is_device_pointer(arrays[i])) {
+         fprintf(stderr, "fusedmm_b200_csr_static_scratch: every array must be in device memory "
+                         "(a host array would need a staging buffer, and this entry point allocates nothing)\n");
+         return FUSEDMM_B200_ERR_ARG;
+      }
+   StaticScratchSlot *slot = nullptr;
+   CKI(static_scratch_base(&slot));
+
+   Params<T> p;
+   memset(&p, 0, sizeof(p));
+   p.val = static_cast<const T *>(a.val);
+   p.indx = a.indx; p.pntrb = a.pntrb; p.pntre = a.pntre;
+   p.x = static_cast<const T *>(a.x); p.y = static_cast<const T *>(a.y); p.z = static_cast<T *>(a.z);
+   p.m = a.m; p.k = a.k; p.ldx = a.ldx; p.ldy = a.ldy; p.ldz = a.ldz;
+   p.ptr64 = a.ptr_bits == 64; p.idx64 = a.idx_bits == 64;
+   p.vop = d.vop; p.rop = d.rop; p.sop = d.sop; p.vsc = d.vsc; p.aop = d.aop;
+   p.sop_kind = sopk.kind;
+   p.sp0 = static_cast<T>(sopk.p0); p.sp1 = static_cast<T>(sopk.p1); p.sp2 = static_cast<T>(sopk.p2);
+   p.accumulate = (g_opt.beta_mode == 0 && d.pattern != PAT_GENERIC) ? (a.beta != 0.0) : 1;
+   p.chunk = std::max<int64_t>(32, g_opt.hub_chunk);
+   p.counter = reinterpret_cast<unsigned long long *>(slot->base);
+   p.hub_row = reinterpret_cast<long long *>(slot->base + STATIC_OFF_HUB_ROW);
+   p.hub_base = reinterpret_cast<long long *>(slot->base + STATIC_OFF_HUB_BASE);
+   p.hub_cap = STATIC_HUB_CAP;
+   p.partials = reinterpret_cast<T *>(slot->base + STATIC_OFF_PARTIALS);
+   p.chunk_cap = static_cast<long long>((FUSEDMM_B200_STATIC_SCRATCH_BYTES - STATIC_OFF_PARTIALS) / (static_cast<size_t>(a.k) * es));
+
+   // Sizes beyond the fixed scratch are refused before anything runs.  The bound needs a truthful nnz:
+   // a row is split only if it has more than `chunk` edges, so at most nnz/chunk rows are split and they
+   // have at most nnz/chunk + (split rows) chunks.
+   if (a.nnz < 0) return FUSEDMM_B200_ERR_ARG;
+   const long long bound_hubs = a.nnz / p.chunk + 1, bound_chunks = a.nnz / p.chunk + bound_hubs;
+   if (bound_hubs > p.hub_cap || bound_chunks > p.chunk_cap) {
+      fprintf(stderr, "fusedmm_b200_csr_static_scratch: nnz = %lld with k = %lld needs room for up to %lld split rows and "
+                      "%lld partial rows; the %u MiB static scratch holds %lld and %lld. Use fusedmm_b200_csr.\n",
+              a.nnz, a.k, bound_hubs, bound_chunks, FUSEDMM_B200_STATIC_SCRATCH_BYTES >> 20, p.hub_cap, p.chunk_cap);
+      return FUSEDMM_B200_ERR_LIMIT;
+   }
+
+   cudaStream_t st = user_stream ? user_stream : cudaStreamLegacy;  // no stream is created
+   if (d.sop == OP_UDEF && sopk.kind == FUSEDMM_SOP_SIGMOID_TABLE_C) {
+      CK(cudaMemcpyAsync(slot->base + STATIC_OFF_TABLE, static_host_sigmoid_table<T>(), SM_TABLE_SIZE * es,
+                         cudaMemcpyHostToDevice, st));
+      p.sop_table = reinterpret_cast<const T *>(slot->base + STATIC_OFF_TABLE);
+   }
+   auto aligned16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+   bool vec_ok = (a.k % W == 0) && (a.ldz % W == 0) && aligned16(p.z) &&
+                 (!need_x || ((a.ldx % W == 0) && aligned16(p.x))) && (!need_y || ((a.ldy % W == 0) && aligned16(p.y)));
+   int G = 0, NV = 0, U = 0;
+   if (vec_ok) {
+      choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
+      if (G == 0) vec_ok = false;
+   }
+   const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
+   const long long rows_per_warp = vec_ok ? 32 / G : 1;
+   const long long row_grid = (a.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
+   const long long hub_grid = static_cast<long long>(slot->sm_count) * 8;
+
+   // the array keeps whatever the previous call left in it: the packed counter is the one word that must
+   // start at zero (hub list and partial sums are rewritten before they are read)
+   CK(cudaMemsetAsync(p.counter, 0, sizeof(unsigned long long), st));
+   scan_hub_rows<<<static_cast<unsigned int>((a.m + 255) / 256), 256, 0, st>>>(
+      p.pntrb, p.pntre, p.ptr64, p.m, p.chunk, p.counter, p.hub_row, p.hub_base, p.hub_cap);
+   p.mode = MODE_HUB_CHUNKS;
+   if (vec_ok) { if (!launch_vec<T>(d.pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, st)) return FUSEDMM_B200_ERR_ARG; }
+   else launch_any<T>(p, WARPS_PER_CTA, hub_grid, st);
+   launch_fixup<T>(p, slot->sm_count, st);
+   p.mode = MODE_ROWS;
+   if (vec_ok) launch_vec<T>(d.pattern, G, NV, U, warps, p, row_grid, st);
+   else launch_any<T>(p, warps, row_grid, st);
+   CK(cudaGetLastError());
+   long long nh = 0, nchunks = 0;
+   if (!user_stream) {
+      unsigned long long packed = 0;
+      CK(cudaMemcpyAsync(&packed, p.counter, sizeof(packed), cudaMemcpyDeviceToHost, st));
+      CK(cudaStreamSynchronize(st));
+      nh = static_cast<long long>(packed >> HUB_SHIFT);
+      nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
+      if (nh > p.hub_cap || nchunks > p.chunk_cap) {  // only possible when nnz understated the edge count
+         fprintf(stderr, "fusedmm_b200_csr_static_scratch: the graph has more split rows than nnz allowed for\n");
+         return FUSEDMM_B200_ERR_LIMIT;
+      }
+   }
+   memset(&t_info, 0, sizeof(t_info));
+   t_info.kernel_launches = 4;
+   t_info.pattern = d.pattern;
+   t_info.lanes_per_edge = vec_ok ? G : 0;
+   t_info.vectors_per_lane = vec_ok ? NV : 0;
+   t_info.hub_rows = nh;
+   t_info.hub_chunks = nchunks;
+   t_info.engine = 1;
+   t_info.sop_kind = d.sop == OP_UDEF ? sopk.kind : -1;
+   return 0;
+}
+
 int32_t letter_to_message(char tkern)
 {
    switch (tkern) {
@@ -917,6 +1094,31 @@ int fusedmm_b200_get_sop(fusedmm_b200_sop *out)
    std::lock_guard<std::mutex> lock(g_mu);
    *out = g_sop;
    return 0;
+}
+
+int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage, int64_t m,
+                                    int64_t n, int64_t k, double alpha, int64_t nnz, int64_t rows, int64_t cols,
+                                    const void *val, const void *indx, const void *pntrb, const void *pntre,
+                                    const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z,
+                                    int64_t ldz, const fusedmm_b200_sop *sop, void *stream)
+{
+   (void)alpha; (void)rows; (void)cols;
+   std::lock_guard<std::mutex> lock(g_mu);
+   if ((dtype != 0 && dtype != 1) || (ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64))
+      return FUSEDMM_B200_ERR_ARG;
+   Decoded d;
+   int st = decode_message(imessage, g_opt, &d);
+   if (st) return st;
+   fusedmm_b200_sop sopk = g_sop;
+   if (d.sop == OP_UDEF && sop) {
+      if (sop->kind < 0 || sop->kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_UDEF;
+      sopk = *sop;
+   }
+   if (m < 0 || k < 0) return FUSEDMM_B200_ERR_ARG;
+   if (d.aop == AOP_NOOP || m == 0 || k == 0) return 0;
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, 0, nullptr};
+   return dtype == 0 ? run_static_scratch<float>(a, d, sopk, static_cast<cudaStream_t>(stream))
+                     : run_static_scratch<double>(a, d, sopk, static_cast<cudaStream_t>(stream));
 }
 
 int fusedmm_b200_stream_status(void)

@@ -196,6 +196,42 @@ int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, in
                            double beta, void *z, int64_t ldz, const fusedmm_b200_sop *sop, void *stream,
                            int32_t n_peers, void *const *z_peers);
 
+/* ------------------------------------------------------------------------------------------------
+ * fusedmm_b200_csr for callers that must not allocate.
+ *
+ * Some hosts of this library may not touch the CUDA allocator once they are running: a serving
+ * process that gave all device memory to its own pool at start-up and would simply get
+ * out-of-memory from cudaMalloc; a real-time loop for which cudaMalloc/cudaFree are off limits
+ * because they may synchronise the whole device and stall every other stream; a plugin sandbox that
+ * is only allowed to launch kernels.  The other entry points keep their split-row scratch (hub list,
+ * per-chunk partial sums) in buffers they cudaMalloc and grow on demand, and create a stream and
+ * events on first use.  This one calls no cudaMalloc, cudaFree, stream/event creation or any other
+ * allocating routine: the same kernels run with their scratch inside a fixed 32 MiB array that is
+ * part of the library image (every GPU the library runs on holds that array from load to exit).
+ *
+ * Same arguments and results as fusedmm_b200_csr, with these limits:
+ *   - every array must already be in device memory (FUSEDMM_B200_ERR_ARG otherwise);
+ *   - nnz must be the true number of edges of the m rows: it is what bounds the scratch. The call is
+ *     refused with FUSEDMM_B200_ERR_LIMIT and a message on stderr when
+ *     nnz/hub_chunk + 1 > 32768 (split rows) or 2*(nnz/hub_chunk) + 1 partial rows of k values do not
+ *     fit in the array, e.g. more than about 16.4 million edges at k = 128 floats (hub_chunk = 512);
+ *   - all launches go to `stream`, or to the legacy default stream when stream is NULL, in which case
+ *     the call returns after they have finished;
+ *   - the first call on a device looks up the array's address on that device; make that first call
+ *     outside any stream capture;
+ *   - the array is shared by all calls on a device and keeps the previous call's contents (the call
+ *     clears the one word that has to start at zero); two calls whose kernels may overlap on the GPU
+ *     (different streams without an ordering between them) race on it and must not be issued.
+ * It has no counterpart in the reference, whose only scratch is a K-element array on each thread's
+ * stack.
+ * ---------------------------------------------------------------------------------------------- */
+int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage,
+                                    int64_t m, int64_t n, int64_t k, double alpha, int64_t nnz,
+                                    int64_t rows, int64_t cols, const void *val, const void *indx,
+                                    const void *pntrb, const void *pntre, const void *x, int64_t ldx,
+                                    const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
+                                    const fusedmm_b200_sop *sop, void *stream);
+
 /* After work enqueued with a non-NULL stream has completed: 0, or FUSEDMM_B200_ERR_LIMIT when the
  * hub-row scratch was too small for that call (the scratch has then been enlarged; run the call again). */
 int fusedmm_b200_stream_status(void);
