@@ -236,17 +236,27 @@ def main():
                 pz = fdist.PeerZ(n, k, tdtype, dev, dist)
                 z = pz.z
                 z.zero_()
-                exchange = "fused: kernels store finished rows into every rank's Z (peer memory), one small all-reduce orders the ranks"
+                if pz.multicast and os.environ.get("FUSEDMM_BENCH_MULTICAST", "1") == "1":
+                    exchange = ("fused: kernels store each finished row once through the NVSwitch multicast mapping of Z "
+                                "(multimem.st), one small all-reduce orders the ranks")
+                else:
+                    exchange = ("fused: kernels store finished rows into every rank's Z (peer memory, one store per peer), "
+                                "one small all-reduce orders the ranks")
             except Exception as exc:  # no symmetric memory on this box: keep the NCCL path
                 pz = None
                 exchange += f" (symmetric memory unavailable: {type(exc).__name__})"
         config["exchange"] = exchange
-    peers = pz.peers_at_row(r0) if pz is not None else None
+    peers = mcast = None
+    if pz is not None:
+        if "multimem" in exchange:
+            mcast = pz.multicast_at_row(r0)
+        else:
+            peers = pz.peers_at_row(r0)
 
     def step():
         st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all[r0:], pe_all[r0:],
                              x[r0:], k, x, k, 0.0, z[r0:], k, sop=sop if sop is not None else 0,
-                             stream=stream.cuda_stream, z_peers=peers)
+                             stream=stream.cuda_stream, z_peers=peers, z_multicast=mcast)
         assert st == 0, api.status_string(st)
         if pz is not None:
             pz.finish_step()
@@ -294,6 +304,14 @@ def main():
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         finite = finite and bool(lo.item() == hi.item())
+        # and it must be what one GPU computes alone (rank 0 recomputes all rows; outside the timed region)
+        if rank == 0:
+            zfull = torch.empty((n, k), dtype=tdtype, device=dev)
+            st = api.fusedMM_csr(msg, n, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all, pe_all, x, k, x, k, 0.0,
+                                 zfull, k, sop=sop if sop is not None else 0)
+            assert st == 0
+            config["exchanged_z_equals_single_gpu_z"] = bool(torch.equal(zfull, z))
+            del zfull
 
     # per-launch CUDA-event times of one synchronous call on this rank's shard
     kms = {"scan": [], "rows": [], "chunks": [], "fixup": [], "main": []}
@@ -395,8 +413,13 @@ def main():
                "gpu_launches": launches_per_step * args.steps, "finite": finite and e2e_ok}
         print(json.dumps(out))
     if world > 1:
+        # leave without tearing down NCCL and the symmetric-memory mappings rank by rank: every rank has
+        # passed the barrier, nothing is in flight, and a plain exit avoids teardown-order hangs
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

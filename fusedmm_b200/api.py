@@ -118,7 +118,7 @@ def _symbol(vt, pt, it):
 
 
 def fusedMM_csr(imessage, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pntre, x, ldx, y, ldy, beta,
-                z, ldz, sop=None, stream=None, z_peers=None):
+                z, ldz, sop=None, stream=None, z_peers=None, z_multicast=None):
     """``fusedMM_csr`` with the reference's argument order and return codes.
 
     ``sop``: ``None`` (process default, see :func:`set_sop`), an ``int`` kind, or ``(kind, p0, p1, p2)``.
@@ -126,7 +126,8 @@ def fusedMM_csr(imessage, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pnt
     array must then be on the device.  With ``sop`` and ``stream`` both ``None`` the call goes through
     the typed symbol (``sfusedMM_csr_i64`` ...), otherwise through ``fusedmm_b200_csr``.
     ``z_peers``: device addresses (``int``) of other GPUs' Z buffers at this call's first row; finished
-    rows are then also stored there (``fusedmm_b200_csr_multi``).
+    rows are then also stored there (``fusedmm_b200_csr_multi``); ``z_multicast``: instead, the NVSwitch
+    multicast address of Z at this call's first row (one ``multimem.st`` per row reaches every GPU).
     """
     L = lib()
     ptrs, dts = zip(*[_describe(a) for a in (val, indx, pntrb, pntre, x, y, z)])
@@ -137,7 +138,7 @@ def fusedMM_csr(imessage, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pnt
     if dts[3] != dts[2]:
         raise TypeError("pntrb and pntre must share one integer type")
     pre, suffix, size_bits = _symbol(vt, dts[2], dts[1] if dts[1] is not None else dts[2])
-    if sop is None and stream is None and not z_peers:
+    if sop is None and stream is None and not z_peers and not z_multicast:
         VT = C.c_float if pre == "s" else C.c_double
         IT = C.c_int32 if size_bits == 32 else C.c_int64
         fn = getattr(L, f"{pre}fusedMM_csr_{suffix}")
@@ -153,13 +154,15 @@ def fusedMM_csr(imessage, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pnt
         spec = C.byref(SopSpec(int(kind), 0, *map(float, params)))
     pb = np.dtype(dts[2]).itemsize * 8
     ib = np.dtype(dts[1]).itemsize * 8 if dts[1] is not None else pb
-    if z_peers:
-        arr = (C.c_void_p * len(z_peers))(*[int(q) for q in z_peers])
+    if z_peers or z_multicast:
+        z_peers = list(z_peers or [])
+        arr = (C.c_void_p * max(1, len(z_peers)))(*[int(q) for q in z_peers])
         fn = L.fusedmm_b200_csr_multi
         fn.restype = C.c_int
-        fn.argtypes = list(L.fusedmm_b200_csr.argtypes) + [C.c_int32, C.c_void_p]
+        fn.argtypes = list(L.fusedmm_b200_csr.argtypes) + [C.c_int32, C.c_void_p, C.c_void_p]
         return fn(0 if pre == "s" else 1, pb, ib, imessage, m, n, k, alpha, nnz, rows, cols, ptrs[0], ptrs[1],
-                  ptrs[2], ptrs[3], ptrs[4], ldx, ptrs[5], ldy, beta, ptrs[6], ldz, spec, stream, len(z_peers), arr)
+                  ptrs[2], ptrs[3], ptrs[4], ldx, ptrs[5], ldy, beta, ptrs[6], ldz, spec, stream, len(z_peers), arr,
+                  int(z_multicast) if z_multicast else None)
     return L.fusedmm_b200_csr(0 if pre == "s" else 1, pb, ib, imessage, m, n, k, alpha, nnz, rows, cols,
                               ptrs[0], ptrs[1], ptrs[2], ptrs[3], ptrs[4], ldx, ptrs[5], ldy, beta, ptrs[6],
                               ldz, spec, stream)

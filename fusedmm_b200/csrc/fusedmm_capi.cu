@@ -387,6 +387,7 @@ struct HostArgs {
    int ptr_bits, idx_bits;
    int n_peers;
    void *const *z_peers;
+   void *z_multicast;
 };
 
 // extent (one past the largest edge position) of indx/val when they have to be staged
@@ -528,7 +529,11 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    p.accumulate = accumulate;
    p.chunk = std::max<int64_t>(32, g_opt.hub_chunk);
    p.n_peers = 0;
-   if (a.n_peers > 0) {
+   p.z_mc = nullptr;
+   if (a.z_multicast) {
+      if (!on_dev[6]) return FUSEDMM_B200_ERR_ARG;
+      p.z_mc = static_cast<T *>(a.z_multicast);
+   } else if (a.n_peers > 0) {
       // finished rows are also stored into the peers' Z buffers (same layout as z): only meaningful for
       // device-resident Z, and only the row scheduler's kernels carry the extra stores
       if (!on_dev[6] || a.n_peers > 8 || !a.z_peers) return FUSEDMM_B200_ERR_ARG;
@@ -555,6 +560,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
                  (!need_x || ((a.ldx % W == 0) && aligned16(p.x))) &&
                  (!need_y || ((a.ldy % W == 0) && aligned16(p.y)));
    for (int i = 0; i < p.n_peers; i++) vec_ok = vec_ok && aligned16(p.z_peer[i]);
+   if (p.z_mc) vec_ok = vec_ok && aligned16(p.z_mc);
    int G = 0, NV = 0, U = 0;
    const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
    if (vec_ok) {
@@ -574,7 +580,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
    // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
    const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
-   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2 && p.n_peers == 0;
+   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2 && p.n_peers == 0 && !p.z_mc;
    p.counter = static_cast<unsigned long long *>(c.counter.ptr);
 
    if (use_stream) {
@@ -739,7 +745,8 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
 int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage, int64_t m, int64_t n,
              int64_t k, int64_t nnz, const void *val, const void *indx, const void *pntrb, const void *pntre,
              const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
-             const fusedmm_b200_sop *sop, void *hook, void *stream, int n_peers = 0, void *const *z_peers = nullptr)
+             const fusedmm_b200_sop *sop, void *hook, void *stream, int n_peers = 0, void *const *z_peers = nullptr,
+             void *z_multicast = nullptr)
 {
    std::lock_guard<std::mutex> lock(g_mu);
    memset(&t_info, 0, sizeof(t_info));
@@ -768,7 +775,7 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
    DeviceCtx *c = nullptr;
    st = get_ctx(&c);
    if (st) return st;
-   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, n_peers, z_peers};
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, n_peers, z_peers, z_multicast};
    return dtype == 0 ? run_typed<float>(*c, a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_typed<double>(*c, a, d, sopk, static_cast<cudaStream_t>(stream));
 }
@@ -1003,12 +1010,12 @@ int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, in
                            const void *val, const void *indx, const void *pntrb, const void *pntre,
                            const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z,
                            int64_t ldz, const fusedmm_b200_sop *sop, void *stream, int32_t n_peers,
-                           void *const *z_peers)
+                           void *const *z_peers, void *z_multicast)
 {
    (void)alpha; (void)rows; (void)cols;
    if (n_peers < 0) return FUSEDMM_B200_ERR_ARG;
    return run_call(dtype, ptr_bits, idx_bits, imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, ldx, y, ldy,
-                   beta, z, ldz, sop, nullptr, stream, n_peers, z_peers);
+                   beta, z, ldz, sop, nullptr, stream, n_peers, z_peers, z_multicast);
 }
 
 #define FMM_DEFINE_CSR(NAME, VT, IT, DT, PB, IB)                                                      \
@@ -1116,7 +1123,7 @@ int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx
    }
    if (m < 0 || k < 0) return FUSEDMM_B200_ERR_ARG;
    if (d.aop == AOP_NOOP || m == 0 || k == 0) return 0;
-   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, 0, nullptr};
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, 0, nullptr, nullptr};
    return dtype == 0 ? run_static_scratch<float>(a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_static_scratch<double>(a, d, sopk, static_cast<cudaStream_t>(stream));
 }

@@ -77,6 +77,10 @@ struct Params {
    // fused into the epilogue); z_peer[i] has the same layout as z
    int n_peers;
    T *z_peer[8];
+   // or: one multicast address of Z (an NVSwitch multicast object that maps the same buffer on every
+   // GPU of the group, this GPU included): a finished row is then stored ONCE with multimem.st and the
+   // switch delivers it to every GPU, so a rank sends its shard once instead of once per peer
+   T *z_mc;
 };
 
 // ---------------------------------------------------------------------------------------------------
@@ -134,6 +138,28 @@ __device__ __forceinline__ void st_vec(T *ptr, const T (&in)[VecOf<T>::W])
 #pragma unroll
    for (int i = 0; i < VecOf<T>::W; i++) e[i] = in[i];
    *reinterpret_cast<V *>(ptr) = v;
+}
+
+// multimem.st: one store through an NVSwitch multicast address lands in every GPU's copy of the buffer
+__device__ __forceinline__ void st_vec_multicast(float *mc, const float (&in)[4])
+{
+   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(in[0]), "f"(in[1]),
+                "f"(in[2]), "f"(in[3]) : "memory");
+}
+__device__ __forceinline__ void st_vec_multicast(double *mc, const double (&in)[2])
+{
+   // multimem.st has no .v2.f64 form; a store only moves bits, so the 16 bytes go as four 32-bit words
+   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
+                "f"(__int_as_float(__double2loint(in[0]))), "f"(__int_as_float(__double2hiint(in[0]))),
+                "f"(__int_as_float(__double2loint(in[1]))), "f"(__int_as_float(__double2hiint(in[1]))) : "memory");
+}
+__device__ __forceinline__ void st_multicast(float *mc, float v)
+{
+   asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_multicast(double *mc, double v)
+{
+   asm volatile("multimem.st.relaxed.sys.global.f64 [%0], %1;" ::"l"(mc), "d"(v) : "memory");
 }
 
 template <typename T> __device__ __forceinline__ T pos_inf();
@@ -463,8 +489,12 @@ fused_vec_kernel(const Params<T> p)
 #pragma unroll
                   for (int i = 0; i < W; i++) acc[v][i] = aop_apply(aop, old[i], acc[v][i]);
                }
-               st_vec(dst + e0, acc[v]);
-               for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
+               if (p.z_mc) {
+                  st_vec_multicast(p.z_mc + w.row * p.ldz + e0, acc[v]);
+               } else {
+                  st_vec(dst + e0, acc[v]);
+                  for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
+               }
             }
          }
       }
@@ -499,9 +529,12 @@ fused_vec_kernel(const Params<T> p)
 #pragma unroll
                   for (int i = 0; i < W; i++) acc[v][i] = aop_apply(aop, old[i], acc[v][i]);
                }
-               st_vec(dst + e0, acc[v]);
-               if (to_z) {
-                  for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
+               if (to_z && p.z_mc) {
+                  st_vec_multicast(p.z_mc + w.row * p.ldz + e0, acc[v]);
+               } else {
+                  st_vec(dst + e0, acc[v]);
+                  if (to_z)
+                     for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
                }
             }
          }
@@ -594,9 +627,13 @@ fused_any_kernel(const Params<T> p)
             if (t < p.k) {
                T r = acc[e];
                if (to_z && p.accumulate) r = aop_apply(aop, dst[t], r);
-               dst[t] = r;
-               if (to_z)
-                  for (int q = 0; q < p.n_peers; q++) p.z_peer[q][w.row * p.ldz + t] = r;
+               if (to_z && p.z_mc) {
+                  st_multicast(p.z_mc + w.row * p.ldz + t, r);
+               } else {
+                  dst[t] = r;
+                  if (to_z)
+                     for (int q = 0; q < p.n_peers; q++) p.z_peer[q][w.row * p.ldz + t] = r;
+               }
             }
          }
       }
@@ -636,8 +673,12 @@ hub_fixup_kernel(const Params<T> p)
       for (long long t = lane; t < p.k; t += 32) {
          T a = p.accumulate ? zr[t] : aop_identity<T>(p.aop);
          for (long long q = 0; q < nch; q++) a = aop_apply(p.aop, a, p.partials[(base + q) * p.k + t]);
-         zr[t] = a;
-         for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = a;
+         if (p.z_mc) {
+            st_multicast(p.z_mc + row * p.ldz + t, a);
+         } else {
+            zr[t] = a;
+            for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = a;
+         }
       }
    }
 }

@@ -63,12 +63,18 @@ class PeerZ:
         self.rank, self.world = self.handle.rank, self.handle.world_size
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         assert self.ptrs[self.rank] == self.z.data_ptr()
+        # NVSwitch multicast mapping of the same buffers (0 when the fabric has none)
+        self.multicast = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.row_bytes = k * self.z.element_size()
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
 
     def peers_at_row(self, r0):
         """Addresses of row ``r0`` in the other ranks' copies of Z."""
         return [p + r0 * self.row_bytes for i, p in enumerate(self.ptrs) if i != self.rank]
+
+    def multicast_at_row(self, r0):
+        """Multicast address of row ``r0`` (None without NVSwitch multicast)."""
+        return self.multicast + r0 * self.row_bytes if self.multicast else None
 
     def finish_step(self):
         """Enqueue the collective that follows this rank's kernels in stream order; when it completes on a
@@ -86,6 +92,7 @@ def fusedMM_csr_fused_exchange(imessage, n, k, val, indx, rowptr, x, y, pz: Peer
     if r1 > r0:
         st = api.fusedMM_csr(imessage, r1 - r0, n, k, 1.0, int(indx.numel()), n, n, val, indx, rowptr[r0:-1],
                              rowptr[r0 + 1:], x[r0:], k, y, k, 0.0, pz.z[r0:], k, sop=sop, stream=stream,
-                             z_peers=pz.peers_at_row(r0))
+                             z_peers=None if pz.multicast else pz.peers_at_row(r0),
+                             z_multicast=pz.multicast_at_row(r0))
     pz.finish_step()
     return st

@@ -187,14 +187,17 @@ int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t 
  * to this call's first row).  The stores are plain global stores that cross NVLink; nothing is read
  * from a peer.  The caller orders the ranks: a peer's rows are complete in this GPU's Z once that peer's
  * call has finished (stream order on the peer) and a cross-rank barrier or collective has been passed.
- * No counterpart in the reference (which is single-process, fusedMM.c:487-744).
+ * z_multicast, when not NULL, replaces the peer list: it is the address, at this call's first row, of
+ * an NVSwitch multicast mapping of Z (it covers this GPU's copy too); each finished row is then stored
+ * once with multimem.st and the switch delivers it to every GPU, so a rank sends its rows once, not
+ * once per peer.  No counterpart in the reference (which is single-process, fusedMM.c:487-744).
  * ---------------------------------------------------------------------------------------------- */
 int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage,
                            int64_t m, int64_t n, int64_t k, double alpha, int64_t nnz, int64_t rows,
                            int64_t cols, const void *val, const void *indx, const void *pntrb,
                            const void *pntre, const void *x, int64_t ldx, const void *y, int64_t ldy,
                            double beta, void *z, int64_t ldz, const fusedmm_b200_sop *sop, void *stream,
-                           int32_t n_peers, void *const *z_peers);
+                           int32_t n_peers, void *const *z_peers, void *z_multicast);
 
 /* ------------------------------------------------------------------------------------------------
  * fusedmm_b200_csr for callers that must not allocate.
