@@ -448,3 +448,51 @@ def test_properties_at_benchmark_size(cuda_device):
     for g in range(4):
         assert call(cfg["msg"], x, z3, sop=cfg["sop"], rows=(int(bounds[g]), int(bounds[g + 1]))) == 0
     assert torch.equal(z1, z3)
+
+
+@pytest.mark.parametrize("name,scale,vt", [("c2_fr_rmat20_k256", 13, np.float32), ("c3_tdist_er4m_k64", 15, np.float32),
+                                           ("c4_spmm_rmat22_k512", 12, np.float32),
+                                           ("c5_sigmoid_rmat24_k128", 14, np.float32),
+                                           ("c5_sigmoid_rmat24_k128", 13, np.float64)])
+def test_benchmark_configs_scaled_down_against_the_oracle(cuda_device, oracle, name, scale, vt):
+    """Configurations 2-5 (same generator, message, SOP, K, value distribution and index widths as the full
+    size, smaller graph) against the CPU oracle, device arrays and host arrays."""
+    import torch
+    dtype = torch.float32 if vt == np.float32 else torch.float64
+    cfg, csr, x = synth.make_config(name, device="cpu", dtype=dtype, scale=scale, ptr_dtype=torch.int64,
+                                    idx_dtype=torch.int32)
+    n, k, sop = csr.n, cfg["k"], cfg["sop"] if cfg["sop"] is not None else 0
+    rp, ix, vl, xs = csr.rowptr.numpy(), csr.indx.numpy(), csr.val.numpy(), x.numpy()
+    want = np.zeros((n, k), vt)
+    assert oracle.csr(cfg["msg"], n, n, k, vl, ix, rp[:-1].copy(), rp[1:].copy(), xs, k, xs, k, 0.0, want, k,
+                      sop_kind=sop) == 0
+    st, z = run_gpu(cuda_device, cfg["msg"], n, n, k, vl, ix, rp[:-1].copy(), rp[1:].copy(), xs, k, xs, k, 0.0,
+                    np.zeros((n, k), vt), k, sop=sop)
+    assert st == 0 and rel_err(z, want) <= RTOL[np.dtype(vt)]
+    zh = np.zeros((n, k), vt)  # the same through host arrays (staged copies, X and Y aliased)
+    assert api.fusedMM_csr(cfg["msg"], n, n, k, 1.0, csr.nnz, n, n, vl, ix, rp[:-1].copy(), rp[1:].copy(), xs, k, xs,
+                           k, 0.0, zh, k, sop=sop) == 0
+    assert np.array_equal(zh, z)
+
+
+def test_properties_at_full_size_of_config_3(cuda_device):
+    """Erdos-Renyi, 4 194 304 vertices, K = 64 (short rows, several per warp): neighbour counts are exact, the
+    t-distribution result is reproducible, finite, and independent of how the rows are sharded."""
+    import torch
+    cfg, csr, x = synth.make_config("c3_tdist_er4m_k64", device=cuda_device)
+    n, k = csr.n, cfg["k"]
+    pb, pe = csr.pntrb.contiguous(), csr.pntre.contiguous()
+    ones = torch.ones((n, k), device=cuda_device)
+    z = torch.empty((n, k), device=cuda_device)
+    assert api.fusedMM_csr(M.MSG_GCN, n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, x, k, ones, k, 0.0, z,
+                           k) == 0
+    assert torch.equal(z, csr.degrees().to(torch.float32)[:, None].expand(n, k))
+    z1, z2 = torch.empty((n, k), device=cuda_device), torch.zeros((n, k), device=cuda_device)
+    assert api.fusedMM_csr(cfg["msg"], n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, x, k, x, k, 0.0, z1, k,
+                           sop=cfg["sop"]) == 0
+    bounds = api.shard_rows(pb.cpu().numpy(), pe.cpu().numpy(), 3)
+    for g in range(3):
+        r0, r1 = int(bounds[g]), int(bounds[g + 1])
+        assert api.fusedMM_csr(cfg["msg"], r1 - r0, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb[r0:], pe[r0:],
+                               x[r0:], k, x, k, 0.0, z2[r0:], k, sop=cfg["sop"]) == 0
+    assert torch.equal(z1, z2) and bool(torch.isfinite(z1).all())
