@@ -225,7 +225,11 @@ def main():
     config.update({"n": n, "nnz": nnz, "sop": sop, "row_shards": [int(b) for b in bounds] if world > 1 else None})
 
     from fusedmm_b200 import dist as fdist
-    stream = torch.cuda.current_stream()
+    # everything that is timed runs on one non-default stream: the library enqueues on it (a NULL stream
+    # would mean a synchronous call), NCCL follows it, and the CUDA events are recorded on it
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    torch.cuda.set_stream(stream)
     # N > 1: the Z exchange is fused into the kernels (stores into the peers' Z over NVLink) when torch's
     # symmetric memory is available on this box, otherwise one NCCL broadcast per row shard follows the kernels
     pz, exchange = None, None

@@ -506,7 +506,8 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       CKI(ensure_buf(c.stage[6], a.m * a.k * es));
       dv[6] = c.stage[6].ptr;
       if (accumulate) {
-         CK(cudaMemcpy2DAsync(c.stage[6].ptr, a.k * es, a.z, a.ldz * es, a.k * es, a.m, cudaMemcpyHostToDevice, st));
+         if (a.ldz == a.k) CK(cudaMemcpyAsync(c.stage[6].ptr, a.z, a.m * a.k * es, cudaMemcpyHostToDevice, st));
+         else CK(cudaMemcpy2DAsync(c.stage[6].ptr, a.k * es, a.z, a.ldz * es, a.k * es, a.m, cudaMemcpyHostToDevice, st));
          h2d += a.m * a.k * es;
       }
    }
@@ -528,6 +529,15 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    p.sp0 = static_cast<T>(sopk.p0); p.sp1 = static_cast<T>(sopk.p1); p.sp2 = static_cast<T>(sopk.p2);
    p.accumulate = accumulate;
    p.chunk = std::max<int64_t>(32, g_opt.hub_chunk);
+   if (a.nnz > 0 && a.nnz < (1ll << 38)) {
+      // Small graphs: cut rows finer so that there are enough work items (about 16 per SM) to fill the
+      // GPU.  nnz is only a hint here (the reference never reads it); a wrong value costs speed, not
+      // correctness.
+      const long long per_item = a.nnz / (static_cast<long long>(c.sm_count) * 16);
+      long long adapt = 128;
+      while (adapt * 2 <= per_item) adapt *= 2;
+      p.chunk = std::min<long long>(p.chunk, std::max<long long>(adapt, 128));
+   }
    p.n_peers = 0;
    p.z_mc = nullptr;
    if (a.z_multicast) {
@@ -721,7 +731,8 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    }
 
    if (!on_dev[6]) {
-      CK(cudaMemcpy2DAsync(a.z, a.ldz * es, c.stage[6].ptr, a.k * es, a.k * es, a.m, cudaMemcpyDeviceToHost, st));
+      if (a.ldz == a.k) CK(cudaMemcpyAsync(a.z, c.stage[6].ptr, a.m * a.k * es, cudaMemcpyDeviceToHost, st));
+      else CK(cudaMemcpy2DAsync(a.z, a.ldz * es, c.stage[6].ptr, a.k * es, a.k * es, a.m, cudaMemcpyDeviceToHost, st));
       CK(cudaStreamSynchronize(st));
       d2h += a.m * a.k * es;
    }

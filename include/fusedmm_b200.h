@@ -265,7 +265,8 @@ int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb
  *                    general kernel (fusedMM.c:698-739).
  *   "accept_vop_noop" 0 (default): VOP_NOOP returns status 2 as in the reference (fusedMM.c:346-377);
  *                    1: VOP_NOOP means T = Y_v.
- *   "hub_chunk"      edges per work item for rows that are split across warps (default 512).
+ *   "hub_chunk"      most edges a row may have before it is split across warps, and edges per piece
+ *                    (default 512; a call whose nnz argument says the graph is small uses less, down to 128).
  *   "force_tiling"   0 = automatic; otherwise (gathers_in_flight << 16) | (lanes_per_edge << 8) |
  *                    vectors_per_lane, gathers_in_flight 0 meaning that tiling's default.
  *   "warps_per_cta"  1..8 (default 1): block size of the main kernel, in warps.

@@ -472,7 +472,8 @@ def test_benchmark_configs_scaled_down_against_the_oracle(cuda_device, oracle, n
     zh = np.zeros((n, k), vt)  # the same through host arrays (staged copies, X and Y aliased)
     assert api.fusedMM_csr(cfg["msg"], n, n, k, 1.0, csr.nnz, n, n, vl, ix, rp[:-1].copy(), rp[1:].copy(), xs, k, xs,
                            k, 0.0, zh, k, sop=sop) == 0
-    assert np.array_equal(zh, z)
+    assert rel_err(zh, want) <= RTOL[np.dtype(vt)]
+    assert rel_err(zh, z) <= RTOL[np.dtype(vt)]  # not bit-equal: the nnz hint of this call splits long rows finer
 
 
 def test_properties_at_full_size_of_config_3(cuda_device):
