@@ -128,6 +128,8 @@ struct DeviceCtx {
    cudaEvent_t evk[4] = {nullptr, nullptr, nullptr, nullptr};  // after scan / rows; start and end of the chunk launch
    cudaStream_t side = nullptr;                 // the chunk and fix-up launches run beside the whole-row launch
    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_side_end = nullptr;
+   cudaStream_t copy = nullptr;                 // copies finished blocks of Z back to the host while later blocks compute
+   cudaEvent_t ev_block[8] = {};
    int sm_count = 148;
    DevBuf stage[7];  // val, indx, pntrb, pntre, x, y, z
    DevBuf counter, hub_row, hub_base, partials;
@@ -199,6 +201,8 @@ int get_ctx(DeviceCtx **out)
       CK(cudaEventCreateWithFlags(&c.ev_fork, cudaEventDisableTiming));
       CK(cudaEventCreateWithFlags(&c.ev_join, cudaEventDisableTiming));
       CK(cudaEventCreate(&c.ev_side_end));
+      CK(cudaStreamCreateWithFlags(&c.copy, cudaStreamNonBlocking));
+      for (auto &e : c.ev_block) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
       CK(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
       CKI(ensure_buf(c.counter, 256));
       c.ready = true;
@@ -399,6 +403,10 @@ long long max_entry(const PT *a, long long m)
    return mx;
 }
 
+constexpr int PIPE_BLOCKS = 8;  // row blocks of the copy-back pipeline (one counter word and one event each)
+template <typename PT>
+int shard_rows(int64_t m, int32_t nshards, const PT *pntrb, const PT *pntre, int64_t *bounds);
+
 template <typename T>
 int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b200_sop &sopk,
               cudaStream_t user_stream)
@@ -585,6 +593,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
 
    int launches = 0;
+   bool z_returned = false;  // the blocked path below has already copied Z back to the host
    float ms = 0.f, ms_k[4] = {0.f, 0.f, 0.f, 0.f}, ms_main = 0.f;
    long long nh = 0, nchunks = 0;
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
@@ -659,44 +668,99 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    const long long row_grid = (a.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
    const long long hub_grid = static_cast<long long>(c.sm_count) * 8;
 
-   for (int attempt = 0; attempt < 3; attempt++) {
-      p.hub_row = static_cast<long long *>(c.hub_row.ptr);
-      p.hub_base = static_cast<long long *>(c.hub_base.ptr);
-      p.hub_cap = c.hub_cap;
-      p.partials = static_cast<T *>(c.partials.ptr);
-      p.chunk_cap = static_cast<long long>(c.partials.bytes / (static_cast<size_t>(a.k) * es));
-
-      if (!async) CK(cudaEventRecord(c.ev0, st));
-      CK(cudaMemsetAsync(c.counter.ptr, 0, sizeof(unsigned long long), st));
-      scan_hub_rows<<<static_cast<unsigned int>((a.m + 255) / 256), 256, 0, st>>>(
-         p.pntrb, p.pntre, p.ptr64, p.m, p.chunk, p.counter, p.hub_row, p.hub_base, p.hub_cap);
+   // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
+   // (and their fix-up) on the side stream beside the whole rows on `st`, forked after the scan and joined
+   // before `st` continues.
+   auto enqueue_pass = [&](Params<T> &q, bool with_rows, bool timing) -> int {
+      const long long qgrid = (q.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
+      CK(cudaMemsetAsync(q.counter, 0, sizeof(unsigned long long), st));
+      scan_hub_rows<<<static_cast<unsigned int>((q.m + 255) / 256), 256, 0, st>>>(
+         q.pntrb, q.pntre, q.ptr64, q.m, q.chunk, q.counter, q.hub_row, q.hub_base, q.hub_cap);
       launches++;
-      if (!async) CK(cudaEventRecord(c.evk[0], st));
-      // The chunks of split rows (and their fix-up) and the whole rows are independent: they run on two
-      // streams, forked after the scan and joined before the call's stream continues.
+      if (timing) CK(cudaEventRecord(c.evk[0], st));
       CK(cudaEventRecord(c.ev_fork, st));
       CK(cudaStreamWaitEvent(c.side, c.ev_fork, 0));
-      if (!async) CK(cudaEventRecord(c.evk[2], c.side));
-      p.mode = MODE_HUB_CHUNKS;
-      if (vec_ok) launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, c.side);
-      else launch_any<T>(p, WARPS_PER_CTA, hub_grid, c.side);
-      if (!async) CK(cudaEventRecord(c.evk[3], c.side));
-      launch_fixup<T>(p, c.sm_count, c.side);
-      if (!async) CK(cudaEventRecord(c.ev_side_end, c.side));
+      if (timing) CK(cudaEventRecord(c.evk[2], c.side));
+      q.mode = MODE_HUB_CHUNKS;
+      if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, q, hub_grid, c.side)) return FUSEDMM_B200_ERR_ARG; }
+      else launch_any<T>(q, WARPS_PER_CTA, hub_grid, c.side);
+      if (timing) CK(cudaEventRecord(c.evk[3], c.side));
+      launch_fixup<T>(q, c.sm_count, c.side);
+      if (timing) CK(cudaEventRecord(c.ev_side_end, c.side));
       CK(cudaEventRecord(c.ev_join, c.side));
       launches += 2;
-      if (attempt == 0) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
-         p.mode = MODE_ROWS;
-         if (vec_ok) {
-            if (!launch_vec<T>(pattern, G, NV, U, warps, p, row_grid, st)) return FUSEDMM_B200_ERR_ARG;
-         } else {
-            launch_any<T>(p, warps, row_grid, st);
-         }
+      if (with_rows) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
+         q.mode = MODE_ROWS;
+         if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, warps, q, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
+         else launch_any<T>(q, warps, qgrid, st);
          launches++;
       }
-      if (!async) CK(cudaEventRecord(c.evk[1], st));
+      if (timing) CK(cudaEventRecord(c.evk[1], st));
       CK(cudaStreamWaitEvent(st, c.ev_join, 0));
       CK(cudaGetLastError());
+      return 0;
+   };
+   auto bind_scratch = [&](Params<T> &q) {
+      q.hub_row = static_cast<long long *>(c.hub_row.ptr);
+      q.hub_base = static_cast<long long *>(c.hub_base.ptr);
+      q.hub_cap = c.hub_cap;
+      q.partials = static_cast<T *>(c.partials.ptr);
+      q.chunk_cap = static_cast<long long>(c.partials.bytes / (static_cast<size_t>(a.k) * es));
+   };
+
+   // ---- Z goes back to a host array: copy it block of rows by block of rows while later blocks compute ----
+   bool rows_done = false;
+   if (!async && !on_dev[6] && !on_dev[2] && !on_dev[3] && static_cast<size_t>(a.m) * a.k * es >= (static_cast<size_t>(32) << 20)) {
+      int64_t bounds[PIPE_BLOCKS + 1];
+      CKI(a.ptr_bits == 64 ? shard_rows(a.m, PIPE_BLOCKS, static_cast<const int64_t *>(a.pntrb), static_cast<const int64_t *>(a.pntre), bounds)
+                           : shard_rows(a.m, PIPE_BLOCKS, static_cast<const int32_t *>(a.pntrb), static_cast<const int32_t *>(a.pntre), bounds));
+      bind_scratch(p);
+      for (int b = 0; b < PIPE_BLOCKS; b++) {
+         const long long r0 = bounds[b], r1 = bounds[b + 1];
+         if (r1 <= r0) continue;
+         Params<T> q = p;
+         q.m = r1 - r0;
+         q.pntrb = static_cast<const char *>(p.pntrb) + r0 * ps;
+         q.pntre = static_cast<const char *>(p.pntre) + r0 * ps;
+         if (q.x) q.x = p.x + r0 * p.ldx;
+         q.z = p.z + r0 * p.ldz;
+         q.counter = p.counter + 2 + b;  // words 0 and 1 belong to the unblocked passes
+         CKI(enqueue_pass(q, true, false));
+         CK(cudaEventRecord(c.ev_block[b], st));
+         CK(cudaStreamWaitEvent(c.copy, c.ev_block[b], 0));
+         const char *src = static_cast<const char *>(c.stage[6].ptr) + static_cast<size_t>(r0) * a.k * es;
+         char *dst = static_cast<char *>(a.z) + static_cast<size_t>(r0) * a.ldz * es;
+         if (a.ldz == a.k) CK(cudaMemcpyAsync(dst, src, static_cast<size_t>(r1 - r0) * a.k * es, cudaMemcpyDeviceToHost, c.copy));
+         else CK(cudaMemcpy2DAsync(dst, a.ldz * es, src, a.k * es, a.k * es, r1 - r0, cudaMemcpyDeviceToHost, c.copy));
+      }
+      unsigned long long words[PIPE_BLOCKS] = {};
+      CK(cudaMemcpyAsync(words, p.counter + 2, sizeof(words), cudaMemcpyDeviceToHost, st));
+      CK(cudaStreamSynchronize(st));
+      CK(cudaStreamSynchronize(c.copy));
+      rows_done = true;
+      bool fits = true;
+      for (int b = 0; b < PIPE_BLOCKS; b++) {
+         const long long bh = static_cast<long long>(words[b] >> HUB_SHIFT), bc = static_cast<long long>(words[b] & HUB_CHUNK_MASK);
+         fits = fits && bh <= p.hub_cap && bc <= p.chunk_cap;
+         nh += bh;
+         nchunks += bc;
+      }
+      if (fits) {
+         z_returned = true;
+         d2h += a.m * a.k * es;
+      } else {  // some block found the scratch too small: redo the split rows of all blocks below, then copy all of Z
+         c.hub_cap = std::max(c.hub_cap, nh + nh / 4 + 1024);
+         CKI(ensure_buf(c.hub_row, c.hub_cap * sizeof(long long)));
+         CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
+         CKI(ensure_buf(c.partials, static_cast<size_t>(nchunks + nchunks / 8 + 64) * a.k * es));
+         nh = nchunks = 0;
+      }
+   }
+
+   for (int attempt = 0; attempt < 3 && !z_returned; attempt++) {
+      bind_scratch(p);
+      if (!async) CK(cudaEventRecord(c.ev0, st));
+      CKI(enqueue_pass(p, attempt == 0 && !rows_done, !async));
       if (async) {
          c.async_pending = true;
          c.async_engine = 1;
@@ -730,7 +794,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    }
    }
 
-   if (!on_dev[6]) {
+   if (!on_dev[6] && !z_returned) {
       if (a.ldz == a.k) CK(cudaMemcpyAsync(a.z, c.stage[6].ptr, a.m * a.k * es, cudaMemcpyDeviceToHost, st));
       else CK(cudaMemcpy2DAsync(a.z, a.ldz * es, c.stage[6].ptr, a.k * es, a.k * es, a.m, cudaMemcpyDeviceToHost, st));
       CK(cudaStreamSynchronize(st));
