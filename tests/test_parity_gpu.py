@@ -500,3 +500,35 @@ def test_properties_at_full_size_of_config_3(cuda_device):
         assert api.fusedMM_csr(cfg["msg"], r1 - r0, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb[r0:], pe[r0:],
                                x[r0:], k, x, k, 0.0, z2[r0:], k, sop=cfg["sop"]) == 0
     assert torch.equal(z1, z2) and bool(torch.isfinite(z1).all())
+
+
+def test_32_bit_indices_with_more_than_2_31_elements_of_y(cuda_device):
+    """Configuration 4 at full size (4 194 304 vertices, K = 512) with every index array int32: n*ldy = 2^31,
+    so `cid*ldy` must be computed in 64 bits (an int32 build of the reference overflows here).  SpMM with the
+    configuration's 1/deg(u) edge values and an all-ones Y must give exactly... 1 for every row that has edges
+    (up to rounding of the sum of deg copies of 1/deg) and 0 for the others; GCN gives the degree exactly."""
+    import torch
+    cfg, csr, _ = synth.make_config("c4_spmm_rmat22_k512", device=cuda_device, ptr_dtype=torch.int32,
+                                    idx_dtype=torch.int32)
+    n, k = csr.n, cfg["k"]
+    assert n * k == 2 ** 31 and csr.rowptr.dtype == torch.int32 and csr.indx.dtype == torch.int32
+    pb, pe = csr.pntrb.contiguous(), csr.pntre.contiguous()
+    ones = torch.ones((n, k), device=cuda_device)
+    z = torch.empty((n, k), device=cuda_device)
+    deg = csr.degrees().to(torch.float32)
+    assert api.fusedMM_csr(M.MSG_GCN, n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, ones, k, ones, k, 0.0,
+                           z, k) == 0
+    assert torch.equal(z[:, 0], deg) and torch.equal(z[:, k - 1], deg) and torch.equal(z[-1], deg[-1].expand(k))
+    assert api.fusedMM_csr(cfg["msg"], n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, ones, k, ones, k, 0.0,
+                           z, k) == 0
+    want = (deg > 0).to(torch.float32)
+    assert float((z[:, 0] - want).abs().max()) <= 1e-4 and float((z[:, k // 2] - want).abs().max()) <= 1e-4
+    # the last rows of Y (element offsets just below 2^31) are really read: make them distinctive
+    y = torch.ones((n, k), device=cuda_device)
+    y[n - 4096:] = 3.0
+    assert api.fusedMM_csr(M.MSG_GCN, n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, y, k, y, k, 0.0, z,
+                           k) == 0
+    hi = torch.zeros(n, device=cuda_device)
+    rows = torch.repeat_interleave(torch.arange(n, device=cuda_device), csr.degrees().to(torch.int64))
+    hi.index_add_(0, rows, (csr.indx >= n - 4096).to(torch.float32))
+    assert torch.equal(z[:, 7], deg + 2.0 * hi)
