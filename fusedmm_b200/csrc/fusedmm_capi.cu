@@ -106,6 +106,29 @@ __global__ void scan_hub_rows(const void *pntrb, const void *pntre, int ptr64, l
    }
 }
 
+// Validation of a CSR: counts rows whose end precedes their start, column ids outside [0, n), edges, and
+// the largest degree.  report[0..3] must be zero on entry.
+__global__ void check_csr_kernel(const void *pntrb, const void *pntre, const void *indx, int ptr64, int idx64,
+                                 long long m, long long n, unsigned long long *report)
+{
+   const int lane = threadIdx.x & 31;
+   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+   unsigned long long bad_rows = 0, bad_cols = 0, edges = 0, maxdeg = 0;
+   for (long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < m; r += nwarps) {
+      const long long b = ld_index(pntrb, r, ptr64), e = ld_index(pntre, r, ptr64);
+      if (e < b || b < 0) { if (lane == 0) bad_rows++; continue; }
+      if (lane == 0) { edges += static_cast<unsigned long long>(e - b); maxdeg = max(maxdeg, static_cast<unsigned long long>(e - b)); }
+      for (long long j = b + lane; j < e; j += 32) {
+         const long long c = ld_index(indx, j, idx64);
+         if (c < 0 || c >= n) bad_cols++;
+      }
+   }
+   if (bad_rows) atomicAdd(report + 0, bad_rows);
+   if (bad_cols) atomicAdd(report + 1, bad_cols);
+   if (edges) atomicAdd(report + 2, edges);
+   if (maxdeg) atomicMax(report + 3, maxdeg);
+}
+
 }  // namespace fmm
 
 namespace {
@@ -172,9 +195,15 @@ thread_local fusedmm_b200_call_info t_info = {};
       if (s_ != 0) return s_;                                                                         \
    } while (0)
 
+int64_t g_fail_alloc_in = 0;  // option "inject_alloc_failure": the n-th device allocation from now on fails
+
 int ensure_buf(DevBuf &b, size_t bytes)
 {
    if (b.bytes >= bytes && b.ptr) return 0;
+   if (g_fail_alloc_in > 0 && --g_fail_alloc_in == 0) {
+      fprintf(stderr, "fusedmm_b200: injected allocation failure (%zu bytes)\n", bytes);
+      return FUSEDMM_B200_ERR_NOMEM;
+   }
    if (b.ptr) CK(cudaFree(b.ptr));
    b.ptr = nullptr;
    b.bytes = 0;
@@ -813,6 +842,12 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    t_info.ms_scan = ms_k[0]; t_info.ms_rows = ms_k[1]; t_info.ms_chunks = ms_k[2]; t_info.ms_fixup = ms_k[3];
    t_info.ms_main = ms_main;
    t_info.sop_kind = d.sop == OP_UDEF ? sopk.kind : -1;
+   static const bool trace = getenv("FUSEDMM_B200_TRACE") != nullptr;
+   if (trace)
+      fprintf(stderr, "fusedmm_b200: msg=%#x %s m=%lld k=%lld engine=%d tiling=%dx%d launches=%d split_rows=%lld chunks=%lld "
+                      "h2d=%lld d2h=%lld B device=%.3f ms (scan %.3f, rows %.3f, chunks %.3f, fix-up %.3f)%s\n",
+              a.imessage, sizeof(T) == 4 ? "f32" : "f64", a.m, a.k, use_stream ? 2 : 1, vec_ok ? G : 0, vec_ok ? NV : 0, launches,
+              nh, nchunks, h2d, d2h, ms, ms_k[0], ms_k[1], ms_k[2], ms_k[3], async ? " [enqueued]" : "");
    return 0;
 }
 
@@ -1236,6 +1271,53 @@ int fusedmm_b200_stream_status(void)
    return FUSEDMM_B200_ERR_LIMIT;
 }
 
+int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_t n, const void *indx,
+                           const void *pntrb, const void *pntre, int64_t *report)
+{
+   std::lock_guard<std::mutex> lock(g_mu);
+   if ((ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64) || m < 0 || !report) return FUSEDMM_B200_ERR_ARG;
+   for (int i = 0; i < 4; i++) report[i] = 0;
+   if (m == 0) return 0;
+   if (!pntrb || !pntre || !indx) return FUSEDMM_B200_ERR_ARG;
+   DeviceCtx *c = nullptr;
+   CKI(get_ctx(&c));
+   const size_t ps = ptr_bits / 8, is = idx_bits / 8;
+   const void *dpb = pntrb, *dpe = pntre, *dix = indx;
+   CK(cudaDeviceSynchronize());
+   if (!is_device_pointer(pntrb)) {
+      CKI(ensure_buf(c->stage[2], m * ps));
+      CK(cudaMemcpyAsync(c->stage[2].ptr, pntrb, m * ps, cudaMemcpyHostToDevice, c->stream));
+      dpb = c->stage[2].ptr;
+   }
+   if (!is_device_pointer(pntre)) {
+      CKI(ensure_buf(c->stage[3], m * ps));
+      CK(cudaMemcpyAsync(c->stage[3].ptr, pntre, m * ps, cudaMemcpyHostToDevice, c->stream));
+      dpe = c->stage[3].ptr;
+   }
+   if (!is_device_pointer(indx)) {
+      std::vector<char> tmp;
+      const void *hpe = pntre;
+      if (is_device_pointer(pntre)) {
+         tmp.resize(m * ps);
+         CK(cudaMemcpy(tmp.data(), pntre, m * ps, cudaMemcpyDeviceToHost));
+         hpe = tmp.data();
+      }
+      const long long ext = ptr_bits == 64 ? max_entry(static_cast<const int64_t *>(hpe), m) : max_entry(static_cast<const int32_t *>(hpe), m);
+      CKI(ensure_buf(c->stage[1], std::max<long long>(ext, 1) * is));
+      CK(cudaMemcpyAsync(c->stage[1].ptr, indx, ext * is, cudaMemcpyHostToDevice, c->stream));
+      dix = c->stage[1].ptr;
+   }
+   unsigned long long *rep = static_cast<unsigned long long *>(c->counter.ptr) + 16;  // words 16..19 of the counter block
+   CK(cudaMemsetAsync(rep, 0, 4 * sizeof(unsigned long long), c->stream));
+   check_csr_kernel<<<c->sm_count * 8, 256, 0, c->stream>>>(dpb, dpe, dix, ptr_bits == 64, idx_bits == 64, m, n, rep);
+   CK(cudaGetLastError());
+   unsigned long long host[4] = {0, 0, 0, 0};
+   CK(cudaMemcpyAsync(host, rep, sizeof(host), cudaMemcpyDeviceToHost, c->stream));
+   CK(cudaStreamSynchronize(c->stream));
+   for (int i = 0; i < 4; i++) report[i] = static_cast<int64_t>(host[i]);
+   return (host[0] || host[1]) ? FUSEDMM_B200_ERR_ARG : 0;
+}
+
 int fusedmm_b200_shard_rows_i32(int64_t m, int32_t nshards, const int32_t *pntrb, const int32_t *pntre, int64_t *bounds)
 {
    return shard_rows(m, nshards, pntrb, pntre, bounds);
@@ -1257,6 +1339,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "engine")) return &g_opt.engine;
    if (!strcmp(name, "edge_quantum")) return &g_opt.edge_quantum;
    if (!strcmp(name, "stream_depth")) return &g_opt.stream_depth;
+   if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
 }
 int fusedmm_b200_set_option(const char *name, int64_t value)

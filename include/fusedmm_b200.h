@@ -255,6 +255,16 @@ int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb
                                 const int64_t *pntre, int64_t *bounds);
 
 /* ------------------------------------------------------------------------------------------------
+ * Validates a CSR on the GPU before it is trusted (the kernels themselves do not bounds-check, like
+ * the reference: fusedMM.c:706-712).  report[0] = rows with pntre < pntrb or pntrb < 0, report[1] =
+ * column ids outside [0, n), report[2] = edges of the m rows, report[3] = largest degree.  Returns 0,
+ * or FUSEDMM_B200_ERR_ARG when report[0] or report[1] is not zero.  Host or device arrays.
+ * No counterpart in the reference (its -DDEBUG build only compares vector dimensions, fusedMM.c:31-37).
+ * ---------------------------------------------------------------------------------------------- */
+int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_t n, const void *indx,
+                           const void *pntrb, const void *pntre, int64_t *report);
+
+/* ------------------------------------------------------------------------------------------------
  * Options, introspection, teardown.
  *
  * fusedmm_b200_set_option(name, value) -> 0, or FUSEDMM_B200_ERR_ARG for an unknown name/value:
@@ -278,7 +288,12 @@ int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb
  *   "stream_depth"   neighbour rows each group of lanes keeps in flight in shared memory (default 16;
  *                    rounded down to a power of two, at least 8 or the lanes per edge if fewer).
  *   "force_generic"  1 = run every message through the flag-interpreting kernel.
+ *   "inject_alloc_failure"  n > 0: the n-th device allocation the library attempts from now on fails
+ *                    with FUSEDMM_B200_ERR_NOMEM (host-side fault injection for tests; nothing is
+ *                    done to the GPU).
  * fusedmm_b200_get_option(name, &value) reads them back.
+ * Environment: FUSEDMM_B200_TRACE (any value) prints one line per call to stderr: message, sizes,
+ * engine and tiling, launches, split rows, bytes copied and the CUDA-event times of the launches.
  * ---------------------------------------------------------------------------------------------- */
 int fusedmm_b200_set_option(const char *name, int64_t value);
 int fusedmm_b200_get_option(const char *name, int64_t *value);

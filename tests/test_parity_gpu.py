@@ -532,3 +532,44 @@ def test_32_bit_indices_with_more_than_2_31_elements_of_y(cuda_device):
     rows = torch.repeat_interleave(torch.arange(n, device=cuda_device), csr.degrees().to(torch.int64))
     hi.index_add_(0, rows, (csr.indx >= n - 4096).to(torch.float32))
     assert torch.equal(z[:, 7], deg + 2.0 * hi)
+
+
+def test_check_csr_and_injected_allocation_failure(cuda_device, oracle):
+    """fusedmm_b200_check_csr finds what the kernels would not (they do not bounds-check, like the reference);
+    a device allocation that fails (injected on the host, nothing is done to the GPU) comes back as
+    FUSEDMM_NOT_ENOUGH_MEM (-1, fusedMM.h:110) and leaves the library usable."""
+    L = api.lib()
+    fn = L.fusedmm_b200_check_csr
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64] + [ctypes.c_void_p] * 4
+    rng = np.random.default_rng(12)
+    m, n, k = 500, 400, 32
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 6, np.int64, np.int32, hub=900)
+    rep = np.zeros(4, np.int64)
+    assert fn(64, 32, m, n, indx.ctypes.data, pntrb.ctypes.data, pntre.ctypes.data, rep.ctypes.data) == 0
+    deg = pntre - pntrb
+    assert list(rep) == [0, 0, int(deg.sum()), int(deg.max())]
+    bad = indx.copy()
+    bad[int(pntrb[3])] = n + 5
+    bad[int(pntrb[m // 3]) + 7] = -1
+    t = dev(bad, cuda_device)
+    assert fn(64, 32, m, n, t.data_ptr(), pntrb.ctypes.data, pntre.ctypes.data, rep.ctypes.data) == M.ERR_ARG
+    assert rep[0] == 0 and rep[1] == 2
+    swapped = pntre.copy()
+    swapped[10] = pntrb[10] - 1
+    assert fn(64, 32, m, n, indx.ctypes.data, pntrb.ctypes.data, swapped.ctypes.data, rep.ctypes.data) == M.ERR_ARG
+    assert rep[0] == 1
+
+    x = np.nan_to_num(dense(rng, max(m, n), k, k, np.float32))
+    val = val.astype(np.float32)
+    L.fusedmm_b200_release()  # so that the next call has to allocate its staging buffers and scratch
+    z = np.zeros((m, k), np.float32)
+    for nth in (1, 3):
+        assert api.set_option("inject_alloc_failure", nth) == 0
+        assert api.fusedMM_csr(M.MSG_SIGMOID, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, k, x, k, 0.0, z,
+                               k) == M.ERR_NOMEM
+        assert api.get_option("inject_alloc_failure") == 0
+    assert api.fusedMM_csr(M.MSG_SIGMOID, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, k, x, k, 0.0, z, k) == 0
+    want = np.zeros((m, k), np.float32)
+    oracle.csr(M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, x, k, x, k, 0.0, want, k, sop_kind=M.SOP_SIGMOID)
+    assert rel_err(z, want) <= 1e-4
