@@ -394,12 +394,13 @@ bool is_device_pointer(const void *p)
 // configurations (K = 64 .. 512, float and double).
 void choose_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
 {
+   // *U also carries the register budget class of the instantiation in bits 8.. (fusedmm_inst.cuh)
    if (nvec <= 4) { *G = 4; *NV = 1; *U = 4; }
    else if (nvec <= 8) { *G = 8; *NV = 1; *U = 8; }
-   else if (nvec <= 16) { *G = 8; *NV = 2; *U = 4; }
+   else if (nvec <= 16) { *G = 8; *NV = 2; *U = 4 | (4 << 8); }
    else if (nvec <= 32) { *G = 16; *NV = 2; *U = 8; }
    else if (nvec <= 64) { *G = 32; *NV = 2; *U = is_double ? 8 : 4; }
-   else if (nvec <= 128) { *G = 32; *NV = 4; *U = 2; }
+   else if (nvec <= 128) { *G = 32; *NV = 4; *U = 2 | (3 << 8); }
    else if (nvec <= 256) { *G = 32; *NV = 8; *U = 1; }
    else { *G = 0; *NV = 0; *U = 0; }
 }
@@ -616,6 +617,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          NV = static_cast<int>(g_opt.force_tiling & 0xFF);
          U = static_cast<int>((g_opt.force_tiling >> 16) & 0xFF);
          if (U == 0) U = default_u(G, NV);
+         U |= static_cast<int>((g_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
       } else choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }

@@ -6,20 +6,20 @@
 
 namespace fmm {
 
-// Row scheduler: (lanes per edge G, 16-byte vectors per lane NV, gathers in flight per slot U).
-// G*NV*16 bytes is the longest row a tiling covers; a lane holds at most 8 gathered vectors.
+// Row scheduler: (lanes per edge G, 16-byte vectors per lane NV, gathers in flight per slot U, register
+// budget class MB).  G*NV*16 bytes is the longest row a tiling covers.
 #define FMM_FOR_EACH_TILING(X) \
-   X(4, 1, 4) X(8, 1, 8) X(8, 2, 4) X(8, 4, 2) X(16, 1, 8) X(16, 2, 4) X(16, 4, 2) \
-   X(32, 1, 8) X(32, 2, 4) X(32, 4, 2) X(32, 8, 1) \
-   X(8, 2, 8) X(16, 2, 8) X(32, 2, 8) X(32, 4, 4)
+   X(4, 1, 4, 0) X(8, 1, 8, 0) X(8, 2, 4, 0) X(8, 4, 2, 0) X(16, 1, 8, 0) X(16, 2, 4, 0) X(16, 4, 2, 0) \
+   X(32, 1, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 0) X(32, 8, 1, 0) \
+   X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3)
 
 // Edge-stream scheduler: (G, NV).
 #define FMM_FOR_EACH_STREAM_TILING(X) \
    X(4, 1) X(8, 1) X(8, 2) X(8, 4) X(16, 1) X(16, 2) X(16, 4) X(32, 1) X(32, 2) X(32, 4) X(32, 8)
 
-#define FMM_TILING_CASE(G_, NV_, U_)                                                                 \
-   case ((U_) << 16) | ((G_) << 8) | (NV_):                                                           \
-      fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_>                                   \
+#define FMM_TILING_CASE(G_, NV_, U_, MB_)                                                            \
+   case ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                                           \
+      fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_>                              \
          <<<static_cast<unsigned int>(grid), warps * 32, 0, stream>>>(p);                             \
       return true;
 
@@ -52,7 +52,10 @@ namespace fmm {
    {                                                                                                  \
       using T_ = T;                                                                                   \
       constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
-      switch ((U << 16) | (G << 8) | NV) {                                                            \
+      /* U carries the register budget class MB in bits 8.. (0 = compiler's choice) */                        \
+      const int MB = U >> 8;                                                                          \
+      U &= 0xFF;                                                                                      \
+      switch ((MB << 24) | (U << 16) | (G << 8) | NV) {                                               \
          FMM_FOR_EACH_TILING(FMM_TILING_CASE)                                                         \
          default: return false;                                                                       \
       }                                                                                               \

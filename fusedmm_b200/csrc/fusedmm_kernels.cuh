@@ -440,8 +440,11 @@ constexpr int WARPS_PER_CTA = 8;  // upper bound; the launch chooses blockDim.x 
 
 // One warp per row (MODE_ROWS) or a grid-stride loop over the chunks of split rows
 // (MODE_HUB_CHUNKS).  Rows longer than p.chunk are skipped in MODE_ROWS.
-template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U>
-__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+// MB = resident 256-thread blocks per SM the register allocation must allow (0: the compiler's choice, 2: at most
+// 128 registers per thread, 3: 80, 4: 64): for some tilings a tighter budget (a few spills, more resident warps)
+// is faster.
+template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U, int MB>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32, MB)
 fused_vec_kernel(const Params<T> p)
 {
    using Eng = VecEngine<T, VOPC, ROPC, VSCC, AOPC, G, NV, U>;

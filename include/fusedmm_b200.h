@@ -277,8 +277,10 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    1: VOP_NOOP means T = Y_v.
  *   "hub_chunk"      most edges a row may have before it is split across warps, and edges per piece
  *                    (default 512; a call whose nnz argument says the graph is small uses less, down to 128).
- *   "force_tiling"   0 = automatic; otherwise (gathers_in_flight << 16) | (lanes_per_edge << 8) |
- *                    vectors_per_lane, gathers_in_flight 0 meaning that tiling's default.
+ *   "force_tiling"   0 = automatic; otherwise (register_budget << 24) | (gathers_in_flight << 16) |
+ *                    (lanes_per_edge << 8) | vectors_per_lane; gathers_in_flight 0 means that tiling's
+ *                    default, register_budget 0 the compiler's choice (only instantiated combinations
+ *                    are accepted, see fusedmm_b200/csrc/fusedmm_inst.cuh).
  *   "warps_per_cta"  1..8 (default 1): block size of the main kernel, in warps.
  *   "engine"         0 or 1 (default): the row scheduler (a warp per row, long rows cut into chunks);
  *                    2: the edge-stream scheduler (equal-sized edge quanta, rows split where the
