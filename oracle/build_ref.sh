@@ -2,13 +2,13 @@
 # Compiles the reference's OWN general kernel (HipGraph/FusedMM fusedMM.c, read where it lies) with
 # oracle/ref_harness.c into oracle/_ref/libfusedmm_ref_<s|d>_<i32|i64>.so.  TEST INFRASTRUCTURE ONLY.
 # No reference source is copied; the only outputs are the shared objects under oracle/_ref/.
-#   usage: oracle/build_ref.sh [reference-dir]      (default /root/reference)
+#   usage: oracle/build_ref.sh [reference-dir]      (default: $FUSEDMM_REFERENCE_DIR, else the read-only mount of the reference)
 # Flags: the macros are the reference's own switches (kernels/CONFIG/make.base:199-223: PTTIME,
 # LOAD_BALANCE, SREAL/DREAL, INDEXTYPE).  -ffp-contract=off keeps mul+add unfused so that the
 # restatement in fusedmm_oracle.c can be required to match bit for bit.
 set -euo pipefail
 here="$(cd "$(dirname "$0")" && pwd)"
-ref="${1:-/root/reference}"
+ref="${1:-${FUSEDMM_REFERENCE_DIR:-/root/reference}}"
 if [ ! -f "$ref/fusedMM.c" ]; then echo "build_ref: no reference at $ref" >&2; exit 3; fi
 out="$here/_ref"; mkdir -p "$out"
 pids=()

@@ -40,7 +40,7 @@ def build_oracle(force: bool = False) -> Path:
     return out
 
 
-def build_reference(reference_dir: str = "/root/reference") -> bool:
+def build_reference(reference_dir: str = os.environ.get("FUSEDMM_REFERENCE_DIR", "/root/reference")) -> bool:
     """Run ``oracle/build_ref.sh`` when the reference sources are present; True if the libraries exist."""
     if Path(reference_dir, "fusedMM.c").exists():
         subprocess.run([str(HERE / "build_ref.sh"), reference_dir], check=True,
