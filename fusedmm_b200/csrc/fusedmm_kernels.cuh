@@ -268,13 +268,19 @@ struct WorkItem {
 };
 
 // largest slot with hub_base[slot] <= item; hub_base is increasing because slot and base come out of
-// one packed atomic counter
+// one packed atomic counter.  The whole warp searches together, 32 pivots per step: four dependent
+// loads for 200 000 split rows instead of eighteen.  Every lane must call this with the same arguments.
 __device__ __forceinline__ long long hub_slot_of(const long long *hub_base, long long nh, long long item)
 {
-   long long lo = 0, hi = nh - 1;
-   while (lo < hi) {
-      long long mid = (lo + hi + 1) >> 1;
-      if (__ldg(hub_base + mid) <= item) lo = mid; else hi = mid - 1;
+   const int lane = threadIdx.x & 31;
+   long long lo = 0, hi = nh;  // the answer is in [lo, hi) and hub_base[lo] <= item
+   while (hi - lo > 1) {
+      const long long step = (hi - lo + 31) / 32;
+      const long long probe = lo + lane * step;
+      const bool le = probe < hi && __ldg(hub_base + probe) <= item;
+      const int cnt = __popc(__ballot_sync(FULL, le));  // the probes that are <= item form a prefix
+      lo += (cnt - 1) * step;
+      hi = lo + step < hi ? lo + step : hi;
    }
    return lo;
 }
