@@ -146,6 +146,44 @@ def host_copies(csr, x):
              "val": csr.val.cpu().numpy()}, x.cpu().numpy())
 
 
+def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n, k, nnz, r0, r1, flops_per_edge, barrier):
+    """The same call through the synchronous typed entry point with pinned HOST arrays: all copies inside."""
+    e2e_steps = args.e2e_steps or max(3, min(args.steps, 8))
+    hv = csr.val.cpu().pin_memory()
+    hi = csr.indx.cpu().pin_memory()
+    hp = csr.rowptr.cpu().pin_memory()
+    hx = x.cpu().pin_memory()
+    hz = torch.zeros((r1 - r0, k), dtype=tdtype).pin_memory()
+    hpb, hpe = hp[:-1], hp[1:]
+
+    def e2e_step():
+        st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, hv, hi, hpb[r0:], hpe[r0:], hx[r0:], k, hx, k, 0.0,
+                             hz, k, sop=sop if sop is not None else 0)
+        assert st == 0, api.status_string(st)
+        return api.call_info()
+
+    # hpb/hpe are views of one pinned tensor, so pntre == pntrb + 1 element and one copy serves both
+    for _ in range(2):
+        einfo = e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        einfo = e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e = {"value": flops_per_edge * nnz / (e2e_ms * 1e-3) * 1e-9, "unit": "GFLOP/s",
+           "h2d_bytes_per_step": int(einfo.h2d_bytes), "d2h_bytes_per_step": int(einfo.d2h_bytes),
+           "ms_per_step": e2e_ms, "timer": "host clock around the synchronous call (copies + kernels), max over ranks",
+           "note": "per rank: its CSR rows' pointers, all column ids, X rows and all of Y in; its Z rows out"}
+    e2e_ok = bool(torch.isfinite(hz).all())
+
+    return e2e, e2e_ok
+
+
 # --------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -158,6 +196,7 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--e2e-steps", type=int, default=None)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-array (end-to-end) leg; e2e is then null")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -351,38 +390,10 @@ def main():
             pass
 
     # ---------------------------------------------------------------- end to end, host buffers
-    e2e_steps = args.e2e_steps or max(3, min(args.steps, 8))
-    hv = csr.val.cpu().pin_memory()
-    hi = csr.indx.cpu().pin_memory()
-    hp = csr.rowptr.cpu().pin_memory()
-    hx = x.cpu().pin_memory()
-    hz = torch.zeros((r1 - r0, k), dtype=tdtype).pin_memory()
-    hpb, hpe = hp[:-1], hp[1:]
-
-    def e2e_step():
-        st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, hv, hi, hpb[r0:], hpe[r0:], hx[r0:], k, hx, k, 0.0,
-                             hz, k, sop=sop if sop is not None else 0)
-        assert st == 0, api.status_string(st)
-        return api.call_info()
-
-    # hpb/hpe are views of one pinned tensor, so pntre == pntrb + 1 element and one copy serves both
-    for _ in range(2):
-        einfo = e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        einfo = e2e_step()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    e2e = {"value": flops_per_edge * nnz / (e2e_ms * 1e-3) * 1e-9, "unit": "GFLOP/s",
-           "h2d_bytes_per_step": int(einfo.h2d_bytes), "d2h_bytes_per_step": int(einfo.d2h_bytes),
-           "ms_per_step": e2e_ms, "timer": "host clock around the synchronous call (copies + kernels), max over ranks",
-           "note": "per rank: its CSR rows' pointers, all column ids, X rows and all of Y in; its Z rows out"}
-    e2e_ok = bool(torch.isfinite(hz).all())
+    e2e, e2e_ok = None, True
+    if not args.no_e2e:
+        e2e, e2e_ok = measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n, k, nnz, r0, r1,
+                                  flops_per_edge, barrier)
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu_baseline = None

@@ -573,3 +573,72 @@ def test_check_csr_and_injected_allocation_failure(cuda_device, oracle):
     want = np.zeros((m, k), np.float32)
     oracle.csr(M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, x, k, x, k, 0.0, want, k, sop_kind=M.SOP_SIGMOID)
     assert rel_err(z, want) <= 1e-4
+
+
+C_CALLER = r"""
+/* A caller of the reference, unchanged: VALUETYPE / INDEXTYPE, the flag macros, its own SOP_UDEF_FUNC. */
+#include <stdio.h>
+#include <stdlib.h>
+#include <stdint.h>
+#include <math.h>
+#define VALUETYPE @VT@
+#define INDEXTYPE @IT@
+#include "fusedMM.h"
+
+int SOP_UDEF_FUNC(VALUETYPE val, VALUETYPE *out) { *out = @SOP@; return FUSEDMM_SUCCESS_RETURN; }
+
+static void *slurp(const char *name, size_t bytes) {
+   void *p = malloc(bytes ? bytes : 1); FILE *f = fopen(name, "rb");
+   if (!f || fread(p, 1, bytes, f) != bytes) { fprintf(stderr, "cannot read %s\n", name); exit(2); }
+   fclose(f); return p;
+}
+int main(int argc, char **argv) {
+   INDEXTYPE m = atol(argv[1]), n = atol(argv[2]), k = atol(argv[3]), nnz = atol(argv[4]);
+   INDEXTYPE *rowptr = slurp("rowptr.bin", (m + 1) * sizeof(INDEXTYPE)), *indx = slurp("indx.bin", nnz * sizeof(INDEXTYPE));
+   VALUETYPE *val = slurp("val.bin", nnz * sizeof(VALUETYPE)), *x = slurp("x.bin", m * k * sizeof(VALUETYPE));
+   VALUETYPE *y = slurp("y.bin", n * k * sizeof(VALUETYPE)), *z = calloc(m * k, sizeof(VALUETYPE));
+   int32_t imsg = 0;
+   SET_VOP_FLAG(imsg, @VOP@); SET_ROP_FLAG(imsg, @ROP@); SET_SOP_FLAG(imsg, SOP_UDEF);
+   SET_VSC_FLAG(imsg, VSC_MUL); SET_AOP_FLAG(imsg, AOP_ADD);
+   int st = fusedMM_csr(imsg, m, n, k, 1.0, nnz, m, n, val, indx, rowptr, rowptr + 1, x, k, y, k, 0.0, z, k);
+   FILE *o = fopen("z.bin", "wb"); fwrite(z, sizeof(VALUETYPE), m * k, o); fclose(o);
+   printf("status %d message %#x\n", st, imsg);
+   return st;
+}
+"""
+
+
+@pytest.mark.parametrize("vt,it,vop,rop,sop_c,sop_kind", [
+    ("float", "int64_t", "VOP_COPY_RHS", "ROP_DOT", "1.0 / (1.0 + exp(-val))", M.SOP_SIGMOID),
+    ("double", "int32_t", "VOP_SUBR", "ROP_NORMR", "1.0 + 1.0 / val", M.SOP_FR)])
+def test_unmodified_c_caller_of_the_reference(cuda_device, oracle, tmp_path, vt, it, vop, rop, sop_c, sop_kind):
+    """The drop-in claim end to end: a C program written against the reference's header (its macros, its own
+    SOP_UDEF_FUNC, host arrays) is compiled against include/fusedMM.h, linked with libfusedmm_b200.so and run."""
+    import subprocess
+    root = Path(__file__).resolve().parents[1]
+    nvt = np.float32 if vt == "float" else np.float64
+    nit = np.int64 if it == "int64_t" else np.int32
+    rng = np.random.default_rng(77)
+    m, n, k = 600, 500, 48
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 9, nit, nit, hub=1500)
+    rowptr = as_rowptr(pntrb, pntre)
+    nnz = int(rowptr[-1])
+    indx, val = indx[:nnz].copy(), val[:nnz].astype(nvt)
+    x, y = np.nan_to_num(dense(rng, m, k, k, nvt)), np.nan_to_num(dense(rng, n, k, k, nvt))
+    for name, a in (("rowptr", rowptr), ("indx", indx), ("val", val), ("x", x), ("y", y)):
+        a.tofile(tmp_path / f"{name}.bin")
+    src = C_CALLER
+    for key, rep in (("@VT@", vt), ("@IT@", it), ("@SOP@", sop_c), ("@VOP@", vop), ("@ROP@", rop)):
+        src = src.replace(key, rep)
+    (tmp_path / "caller.c").write_text(src)
+    libdir = api.LIB_PATH.parent
+    subprocess.run(["gcc", "-O1", "caller.c", f"-I{root / 'include'}", f"-L{libdir}", "-lfusedmm_b200",
+                    f"-Wl,-rpath,{libdir}", "-lm", "-o", "caller"], cwd=tmp_path, check=True)
+    run = subprocess.run(["./caller", str(m), str(n), str(k), str(nnz)], cwd=tmp_path, capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    msg = M.MSG_SIGMOID if rop == "ROP_DOT" else M.MSG_TDIST
+    assert f"message {msg:#x}" in run.stdout
+    z = np.fromfile(tmp_path / "z.bin", dtype=nvt).reshape(m, k)
+    want = np.zeros((m, k), nvt)
+    oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop_kind)
+    assert rel_err(z, want) <= RTOL[np.dtype(nvt)]
