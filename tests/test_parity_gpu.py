@@ -642,3 +642,17 @@ def test_unmodified_c_caller_of_the_reference(cuda_device, oracle, tmp_path, vt,
     want = np.zeros((m, k), nvt)
     oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop_kind)
     assert rel_err(z, want) <= RTOL[np.dtype(nvt)]
+
+
+def test_generators_give_the_same_graph_on_cpu_and_gpu(cuda_device):
+    cpu = synth.rmat_edges(12, 16, seed=9)
+    gpu = synth.rmat_edges(12, 16, seed=9, device=cuda_device)
+    assert all(torch_equal(a, b.cpu()) for a, b in zip(cpu, gpu))
+    a = synth.dense_uniform(300, 64, -1.0, 1.0, seed=4)
+    b = synth.dense_uniform(300, 64, -1.0, 1.0, seed=4, device=cuda_device)
+    assert torch_equal(a, b.cpu())
+
+
+def torch_equal(a, b):
+    import torch
+    return torch.equal(a, b)
