@@ -695,6 +695,25 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
    }
    if (c.partials.bytes == 0) CKI(ensure_buf(c.partials, static_cast<size_t>(64) << 20));
+   if (a.nnz > 0 && a.nnz < (1ll << 38)) {
+      // With a truthful nnz the scratch can be sized before anything runs (a row is split only if it has
+      // more than `chunk` edges), so that a call enqueued on a caller's stream never finds it too small.
+      // nnz stays a hint: if it understates the graph the overflow path below still catches it.
+      const long long bound_hubs = a.nnz / p.chunk + 1, bound_chunks = a.nnz / p.chunk + bound_hubs;
+      const size_t want = static_cast<size_t>(bound_chunks) * a.k * es;
+      if (bound_hubs > c.hub_cap || want > c.partials.bytes) {
+         size_t free_b = 0, total_b = 0;
+         CK(cudaMemGetInfo(&free_b, &total_b));
+         if (static_cast<double>(want) < 0.25 * static_cast<double>(free_b)) {
+            if (bound_hubs > c.hub_cap) {
+               c.hub_cap = bound_hubs;
+               CKI(ensure_buf(c.hub_row, c.hub_cap * sizeof(long long)));
+               CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
+            }
+            CKI(ensure_buf(c.partials, want));
+         }
+      }
+   }
    const long long rows_per_warp = vec_ok ? 32 / G : 1;  // short rows: one per group of G lanes
    const long long row_grid = (a.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
    const long long hub_grid = static_cast<long long>(c.sm_count) * 8;

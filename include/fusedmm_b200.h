@@ -169,8 +169,10 @@ FUSEDMM_B200_DECL_G(dgfusedMM_csr_i64, double, int64_t);
  *   stream    NULL = run on the library's own stream and return when Z is complete.
  *             Otherwise a cudaStream_t: all work is enqueued on it and the call returns without
  *             waiting; every array must then be a device pointer (else FUSEDMM_B200_ERR_ARG), and
- *             a capacity overflow of the hub-row scratch is reported by the next synchronous call
- *             or by fusedmm_b200_stream_status().
+ *             a capacity overflow of the split-row scratch (only possible when nnz understates the
+ *             graph: a positive nnz sizes the scratch before the launches) is reported by
+ *             fusedmm_b200_stream_status().  The scratch is per device: calls enqueued on different
+ *             streams of one device must be ordered by the caller.
  * Everything else: as fusedMM_csr (fusedMM.h:76-97).
  * ---------------------------------------------------------------------------------------------- */
 int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage,
