@@ -199,3 +199,53 @@ def shard_rows(pntrb, pntre, nshards):
     if st:
         raise FusedMMError(status_string(st))
     return bounds
+
+
+class Plan:
+    """``fusedmm_b200_plan_*``: the CSR kept on the device together with its split-row list, for many calls over
+    one graph.  ``indx``, ``pntrb``, ``pntre`` (and optionally ``val``) are NumPy arrays or torch tensors; device
+    tensors are borrowed and must outlive the plan."""
+
+    def __init__(self, indx, pntrb, pntre, val=None):
+        L = lib()
+        ptrs, dts = zip(*[_describe(a) for a in (val, indx, pntrb, pntre)])
+        self._keep = (val, indx, pntrb, pntre)
+        self.m = len(pntrb)
+        pb, ib = np.dtype(dts[2]).itemsize * 8, np.dtype(dts[1]).itemsize * 8
+        vd = -1 if val is None else (0 if np.dtype(dts[0]) == np.float32 else 1)
+        self._h = C.c_void_p()
+        fn = L.fusedmm_b200_plan_create
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                       C.c_void_p, C.POINTER(C.c_void_p)]
+        st = fn(pb, ib, self.m, 0, ptrs[1], ptrs[2], ptrs[3], vd, ptrs[0], C.byref(self._h))
+        if st:
+            raise FusedMMError(status_string(st))
+
+    def csr(self, imessage, n, k, x, ldx, y, ldy, beta, z, ldz, sop=None, stream=None):
+        """``fusedmm_b200_plan_csr``: the call without the CSR arguments; returns the status code."""
+        L = lib()
+        ptrs, dts = zip(*[_describe(a) for a in (x, y, z)])
+        dtype = 0 if np.dtype(dts[2]) == np.float32 else 1
+        spec = None
+        if sop is not None:
+            kind, *params = (sop,) if isinstance(sop, int) else tuple(sop)
+            params = list(params) + [0.0] * (3 - len(params))
+            spec = C.byref(SopSpec(int(kind), 0, *map(float, params)))
+        fn = L.fusedmm_b200_plan_csr
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                       C.c_int64, C.c_double, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+        return fn(self._h, dtype, imessage, n, k, ptrs[0], ldx, ptrs[1], ldy, beta, ptrs[2], ldz, spec, stream)
+
+    def close(self):
+        if self._h:
+            lib().fusedmm_b200_plan_destroy.argtypes = [C.c_void_p]
+            lib().fusedmm_b200_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

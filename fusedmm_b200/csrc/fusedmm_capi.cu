@@ -17,6 +17,18 @@
 #include <mutex>
 #include <vector>
 
+// The inspector's result (fusedmm_b200_plan_create): the CSR resident on one device and its split-row list.
+struct fusedmm_b200_plan {
+   int device = -1;
+   int ptr_bits = 64, idx_bits = 32, val_dtype = -1;  // val_dtype: -1 no values, 0 float, 1 double
+   long long m = 0, nnz = 0, chunk = 512;
+   void *own[4] = {nullptr, nullptr, nullptr, nullptr};  // device copies made from host arrays (val, indx, pntrb, pntre)
+   const void *val = nullptr, *indx = nullptr, *pntrb = nullptr, *pntre = nullptr;  // device addresses used by the calls
+   long long *hub_row = nullptr, *hub_base = nullptr;
+   unsigned long long *counter = nullptr;  // packed (split rows << 40) | chunks, written once by the scan
+   long long nh = 0, nchunks = 0;
+};
+
 namespace fmm {
 
 // per-pattern launchers (inst_*.cu)
@@ -422,6 +434,7 @@ struct HostArgs {
    int n_peers;
    void *const *z_peers;
    void *z_multicast;
+   const fusedmm_b200_plan *plan;
 };
 
 // extent (one past the largest edge position) of indx/val when they have to be staged
@@ -576,6 +589,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       while (adapt * 2 <= per_item) adapt *= 2;
       p.chunk = std::min<long long>(p.chunk, std::max<long long>(adapt, 128));
    }
+   if (a.plan) p.chunk = a.plan->chunk;  // the split-row list of a plan was made for this chunk size
    p.n_peers = 0;
    p.z_mc = nullptr;
    if (a.z_multicast) {
@@ -630,7 +644,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
    // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
    const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
-   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2 && p.n_peers == 0 && !p.z_mc;
+   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2 && p.n_peers == 0 && !p.z_mc && !a.plan;
    p.counter = static_cast<unsigned long long *>(c.counter.ptr);
 
    if (use_stream) {
@@ -695,7 +709,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
    }
    if (c.partials.bytes == 0) CKI(ensure_buf(c.partials, static_cast<size_t>(64) << 20));
-   if (a.nnz > 0 && a.nnz < (1ll << 38)) {
+   if (!a.plan && a.nnz > 0 && a.nnz < (1ll << 38)) {
       // With a truthful nnz the scratch can be sized before anything runs (a row is split only if it has
       // more than `chunk` edges), so that a call enqueued on a caller's stream never finds it too small.
       // nnz stays a hint: if it understates the graph the overflow path below still catches it.
@@ -723,10 +737,12 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // before `st` continues.
    auto enqueue_pass = [&](Params<T> &q, bool with_rows, bool timing) -> int {
       const long long qgrid = (q.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
-      CK(cudaMemsetAsync(q.counter, 0, sizeof(unsigned long long), st));
-      scan_hub_rows<<<static_cast<unsigned int>((q.m + 255) / 256), 256, 0, st>>>(
-         q.pntrb, q.pntre, q.ptr64, q.m, q.chunk, q.counter, q.hub_row, q.hub_base, q.hub_cap);
-      launches++;
+      if (!a.plan) {  // a plan carries the result of this scan
+         CK(cudaMemsetAsync(q.counter, 0, sizeof(unsigned long long), st));
+         scan_hub_rows<<<static_cast<unsigned int>((q.m + 255) / 256), 256, 0, st>>>(
+            q.pntrb, q.pntre, q.ptr64, q.m, q.chunk, q.counter, q.hub_row, q.hub_base, q.hub_cap);
+         launches++;
+      }
       if (timing) CK(cudaEventRecord(c.evk[0], st));
       CK(cudaEventRecord(c.ev_fork, st));
       CK(cudaStreamWaitEvent(c.side, c.ev_fork, 0));
@@ -751,16 +767,18 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       return 0;
    };
    auto bind_scratch = [&](Params<T> &q) {
-      q.hub_row = static_cast<long long *>(c.hub_row.ptr);
-      q.hub_base = static_cast<long long *>(c.hub_base.ptr);
-      q.hub_cap = c.hub_cap;
+      q.hub_row = a.plan ? a.plan->hub_row : static_cast<long long *>(c.hub_row.ptr);
+      q.hub_base = a.plan ? a.plan->hub_base : static_cast<long long *>(c.hub_base.ptr);
+      q.hub_cap = a.plan ? std::max<long long>(a.plan->nh, 1) : c.hub_cap;
+      if (a.plan) q.counter = a.plan->counter;
       q.partials = static_cast<T *>(c.partials.ptr);
       q.chunk_cap = static_cast<long long>(c.partials.bytes / (static_cast<size_t>(a.k) * es));
    };
 
    // ---- Z goes back to a host array: copy it block of rows by block of rows while later blocks compute ----
    bool rows_done = false;
-   if (!async && !on_dev[6] && !on_dev[2] && !on_dev[3] && static_cast<size_t>(a.m) * a.k * es >= (static_cast<size_t>(32) << 20)) {
+   if (a.plan) CKI(ensure_buf(c.partials, static_cast<size_t>(std::max<long long>(a.plan->nchunks, 1)) * a.k * es));
+   if (!a.plan && !async && !on_dev[6] && !on_dev[2] && !on_dev[3] && static_cast<size_t>(a.m) * a.k * es >= (static_cast<size_t>(32) << 20)) {
       int64_t bounds[PIPE_BLOCKS + 1];
       CKI(a.ptr_bits == 64 ? shard_rows(a.m, PIPE_BLOCKS, static_cast<const int64_t *>(a.pntrb), static_cast<const int64_t *>(a.pntre), bounds)
                            : shard_rows(a.m, PIPE_BLOCKS, static_cast<const int32_t *>(a.pntrb), static_cast<const int32_t *>(a.pntre), bounds));
@@ -812,15 +830,17 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       if (!async) CK(cudaEventRecord(c.ev0, st));
       CKI(enqueue_pass(p, attempt == 0 && !rows_done, !async));
       if (async) {
-         c.async_pending = true;
-         c.async_engine = 1;
-         c.async_k = a.k;
-         c.async_elt = es;
+         if (!a.plan) {  // the scratch of a plan call is sized exactly: nothing to report later
+            c.async_pending = true;
+            c.async_engine = 1;
+            c.async_k = a.k;
+            c.async_elt = es;
+         }
          break;
       }
       CK(cudaEventRecord(c.ev1, st));
       unsigned long long packed = 0;
-      CK(cudaMemcpyAsync(&packed, c.counter.ptr, sizeof(packed), cudaMemcpyDeviceToHost, st));
+      CK(cudaMemcpyAsync(&packed, p.counter, sizeof(packed), cudaMemcpyDeviceToHost, st));
       CK(cudaStreamSynchronize(st));
       float t = 0.f;
       CK(cudaEventElapsedTime(&t, c.ev0, c.ev1));
@@ -877,7 +897,7 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
              int64_t k, int64_t nnz, const void *val, const void *indx, const void *pntrb, const void *pntre,
              const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
              const fusedmm_b200_sop *sop, void *hook, void *stream, int n_peers = 0, void *const *z_peers = nullptr,
-             void *z_multicast = nullptr)
+             void *z_multicast = nullptr, const fusedmm_b200_plan *plan = nullptr)
 {
    std::lock_guard<std::mutex> lock(g_mu);
    memset(&t_info, 0, sizeof(t_info));
@@ -906,7 +926,7 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
    DeviceCtx *c = nullptr;
    st = get_ctx(&c);
    if (st) return st;
-   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, n_peers, z_peers, z_multicast};
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, n_peers, z_peers, z_multicast, plan};
    return dtype == 0 ? run_typed<float>(*c, a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_typed<double>(*c, a, d, sopk, static_cast<cudaStream_t>(stream));
 }
@@ -1254,9 +1274,103 @@ int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx
    }
    if (m < 0 || k < 0) return FUSEDMM_B200_ERR_ARG;
    if (d.aop == AOP_NOOP || m == 0 || k == 0) return 0;
-   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, 0, nullptr, nullptr};
+   HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, 0, nullptr, nullptr, nullptr};
    return dtype == 0 ? run_static_scratch<float>(a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_static_scratch<double>(a, d, sopk, static_cast<cudaStream_t>(stream));
+}
+
+int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_t nnz, const void *indx,
+                             const void *pntrb, const void *pntre, int32_t val_dtype, const void *val,
+                             fusedmm_b200_plan **out)
+{
+   (void)nnz;
+   std::lock_guard<std::mutex> lock(g_mu);
+   if (!out || m < 0 || (ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64) ||
+       (val && val_dtype != 0 && val_dtype != 1) || (m > 0 && (!pntrb || !pntre)))
+      return FUSEDMM_B200_ERR_ARG;
+   *out = nullptr;
+   DeviceCtx *c = nullptr;
+   CKI(get_ctx(&c));
+   CK(cudaDeviceSynchronize());
+   fusedmm_b200_plan *pl = new fusedmm_b200_plan();
+   pl->device = c->device;
+   pl->ptr_bits = ptr_bits; pl->idx_bits = idx_bits; pl->val_dtype = val ? val_dtype : -1; pl->m = m;
+   const size_t ps = ptr_bits / 8, is = idx_bits / 8, vs = val_dtype == 1 ? 8 : 4;
+   auto fail = [&](int st) { fusedmm_b200_plan_destroy(pl); return st; };
+   // the edge extent of the arrays: largest row end
+   long long ext = 0;
+   if (m > 0) {
+      std::vector<char> tmp;
+      const void *hpe = pntre;
+      if (is_device_pointer(pntre)) {
+         tmp.resize(m * ps);
+         if (cudaMemcpy(tmp.data(), pntre, m * ps, cudaMemcpyDeviceToHost) != cudaSuccess) return fail(FUSEDMM_B200_ERR_CUDA);
+         hpe = tmp.data();
+      }
+      ext = ptr_bits == 64 ? max_entry(static_cast<const int64_t *>(hpe), m) : max_entry(static_cast<const int32_t *>(hpe), m);
+   }
+   pl->nnz = ext;
+   const void *src[4] = {val, indx, pntrb, pntre};
+   const size_t bytes[4] = {static_cast<size_t>(ext) * vs, static_cast<size_t>(ext) * is, static_cast<size_t>(m) * ps, static_cast<size_t>(m) * ps};
+   const void **dst[4] = {&pl->val, &pl->indx, &pl->pntrb, &pl->pntre};
+   const bool pe_is_pb1 = pntrb && static_cast<const char *>(pntre) == static_cast<const char *>(pntrb) + ps;
+   for (int i = 0; i < 4; i++) {
+      if (!src[i]) continue;
+      if (is_device_pointer(src[i])) { *dst[i] = src[i]; continue; }  // borrowed: the caller keeps it alive
+      if (i == 3 && pe_is_pb1 && pl->own[2]) { pl->pntre = static_cast<const char *>(pl->own[2]) + ps; continue; }
+      const size_t nb = (i == 2 && pe_is_pb1) ? bytes[i] + ps : bytes[i];  // (rowptr, rowptr+1): one copy of m+1 entries
+      if (cudaMalloc(&pl->own[i], std::max<size_t>(nb, 16)) != cudaSuccess) { cudaGetLastError(); return fail(FUSEDMM_B200_ERR_NOMEM); }
+      if (nb && cudaMemcpy(pl->own[i], src[i], nb, cudaMemcpyHostToDevice) != cudaSuccess) return fail(FUSEDMM_B200_ERR_CUDA);
+      *dst[i] = pl->own[i];
+   }
+   // split-row list, sized by its upper bound so that the scan cannot overflow it
+   pl->chunk = std::max<int64_t>(32, g_opt.hub_chunk);
+   if (ext > 0) {
+      const long long per_item = ext / (static_cast<long long>(c->sm_count) * 16);
+      long long adapt = 128;
+      while (adapt * 2 <= per_item) adapt *= 2;
+      pl->chunk = std::min<long long>(pl->chunk, std::max<long long>(adapt, 128));
+   }
+   const long long cap = ext / pl->chunk + 1;
+   if (cudaMalloc(&pl->hub_row, cap * sizeof(long long)) != cudaSuccess || cudaMalloc(&pl->hub_base, cap * sizeof(long long)) != cudaSuccess ||
+       cudaMalloc(&pl->counter, 256) != cudaSuccess) { cudaGetLastError(); return fail(FUSEDMM_B200_ERR_NOMEM); }
+   if (cudaMemset(pl->counter, 0, 256) != cudaSuccess) return fail(FUSEDMM_B200_ERR_CUDA);
+   if (m > 0) {
+      scan_hub_rows<<<static_cast<unsigned int>((m + 255) / 256), 256, 0, c->stream>>>(pl->pntrb, pl->pntre, ptr_bits == 64, m, pl->chunk,
+                                                                                     pl->counter, pl->hub_row, pl->hub_base, cap);
+      unsigned long long packed = 0;
+      if (cudaMemcpyAsync(&packed, pl->counter, sizeof(packed), cudaMemcpyDeviceToHost, c->stream) != cudaSuccess ||
+          cudaStreamSynchronize(c->stream) != cudaSuccess) return fail(FUSEDMM_B200_ERR_CUDA);
+      pl->nh = static_cast<long long>(packed >> HUB_SHIFT);
+      pl->nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
+   }
+   *out = pl;
+   return 0;
+}
+
+int fusedmm_b200_plan_csr(const fusedmm_b200_plan *plan, int32_t dtype, int32_t imessage, int64_t n, int64_t k,
+                          const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
+                          const fusedmm_b200_sop *sop, void *stream)
+{
+   if (!plan) return FUSEDMM_B200_ERR_ARG;
+   int dev = -1;
+   if (cudaGetDevice(&dev) != cudaSuccess || dev != plan->device) return FUSEDMM_B200_ERR_ARG;
+   const bool uses_val = ((imessage >> 4) & 0xF) == 0 && ((imessage >> 12) & 0xF) != 0;
+   if (uses_val && plan->val_dtype != dtype) return FUSEDMM_B200_ERR_ARG;  // edge values of the other type, or none
+   return run_call(dtype, plan->ptr_bits, plan->idx_bits, imessage, plan->m, n, k, plan->nnz, plan->val, plan->indx,
+                   plan->pntrb, plan->pntre, x, ldx, y, ldy, beta, z, ldz, sop, nullptr, stream, 0, nullptr, nullptr, plan);
+}
+
+int fusedmm_b200_plan_destroy(fusedmm_b200_plan *plan)
+{
+   if (!plan) return 0;
+   cudaDeviceSynchronize();
+   for (void *q : plan->own) if (q) cudaFree(q);
+   if (plan->hub_row) cudaFree(plan->hub_row);
+   if (plan->hub_base) cudaFree(plan->hub_base);
+   if (plan->counter) cudaFree(plan->counter);
+   delete plan;
+   return 0;
 }
 
 int fusedmm_b200_stream_status(void)

@@ -237,6 +237,28 @@ int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx
                                     const void *y, int64_t ldy, double beta, void *z, int64_t ldz,
                                     const fusedmm_b200_sop *sop, void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Inspector / executor split for callers that run many messages over one fixed graph (the epochs of
+ * an embedding or GNN training loop).  The reference redoes its row partition in every thread on every
+ * call (fusedMM.c:633-676) and its timers anticipate "an inspector phase" (test/fusedMMtime.cpp:1483-1485).
+ *
+ * fusedmm_b200_plan_create copies host CSR arrays to the current device once (device arrays are
+ * borrowed: keep them alive and unchanged while the plan lives), finds the rows that have to be split and
+ * keeps that list.  val may be NULL (val_dtype ignored) for graphs used only with messages that do not
+ * read edge values; val_dtype: 0 float, 1 double.  nnz is ignored (the extent is the largest row end).
+ * fusedmm_b200_plan_csr is fusedmm_b200_csr without the CSR arguments: x, y, z may be host or device
+ * arrays, stream as in fusedmm_b200_csr.  Per call it saves the scan launch and, for host callers, the copy
+ * of the column ids and edge values.  A plan belongs to the device it was created on.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fusedmm_b200_plan fusedmm_b200_plan;
+int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_t nnz, const void *indx,
+                             const void *pntrb, const void *pntre, int32_t val_dtype, const void *val,
+                             fusedmm_b200_plan **out);
+int fusedmm_b200_plan_csr(const fusedmm_b200_plan *plan, int32_t dtype, int32_t imessage, int64_t n, int64_t k,
+                          const void *x, int64_t ldx, const void *y, int64_t ldy, double beta, void *z,
+                          int64_t ldz, const fusedmm_b200_sop *sop, void *stream);
+int fusedmm_b200_plan_destroy(fusedmm_b200_plan *plan);
+
 /* After work enqueued with a non-NULL stream has completed: 0, or FUSEDMM_B200_ERR_LIMIT when the
  * hub-row scratch was too small for that call (the scratch has then been enlarged; run the call again). */
 int fusedmm_b200_stream_status(void);

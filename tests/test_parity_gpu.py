@@ -656,3 +656,73 @@ def test_generators_give_the_same_graph_on_cpu_and_gpu(cuda_device):
 def torch_equal(a, b):
     import torch
     return torch.equal(a, b)
+
+
+def test_plan_gives_the_same_bits_as_the_direct_call(cuda_device, oracle):
+    """Inspector/executor split: the CSR staged once, the split-row list kept; every call through the plan
+    equals the direct call bit for bit (same kernels, same chunking), for device and host arrays, with and
+    without edge values, synchronous and on a stream."""
+    import torch
+    rng = np.random.default_rng(41)
+    m, n, k = 2500, 2000, 128
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 11, np.int64, np.int32, hub=4000)
+    rowptr = as_rowptr(pntrb, pntre)
+    nnz = int(rowptr[-1])
+    val = val[:nnz].astype(np.float32)
+    indx = indx[:nnz].copy()
+    x, y = np.nan_to_num(dense(rng, m, k, k, np.float32)), np.nan_to_num(dense(rng, n, k, k, np.float32))
+    plan = api.Plan(indx, rowptr[:-1], rowptr[1:], val)          # host CSR: copied to the device once
+    for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_TDIST, M.SOP_FR), (M.MSG_SPMM, 0), (M.MSG_GCN, 0)):
+        want = np.zeros((m, k), np.float32)
+        oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop)
+        zd = np.zeros((m, k), np.float32)
+        assert api.fusedMM_csr(msg, m, n, k, 1.0, nnz, m, n, val, indx, rowptr[:-1], rowptr[1:], x, k, y, k, 0.0, zd, k,
+                               sop=sop) == 0
+        direct_launches = api.call_info().kernel_launches
+        zp = np.zeros((m, k), np.float32)
+        assert plan.csr(msg, n, k, x, k, y, k, 0.0, zp, k, sop=sop) == 0
+        info = api.call_info()
+        assert info.kernel_launches == direct_launches - 1 and info.hub_rows >= 1   # no scan launch
+        assert info.h2d_bytes == (x.nbytes if msg in (M.MSG_SIGMOID, M.MSG_TDIST) else 0) + y.nbytes  # no CSR copy
+        assert np.array_equal(zp, zd) and rel_err(zp, want) <= 1e-4
+        # device arrays, enqueued on a stream
+        tx, ty, tz = dev(x, cuda_device), dev(y, cuda_device), torch.zeros((m, k), device=cuda_device)
+        s = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s):
+            assert plan.csr(msg, n, k, tx, k, ty, k, 0.0, tz, k, sop=sop, stream=s.cuda_stream) == 0
+        s.synchronize()
+        assert np.array_equal(tz.cpu().numpy(), zd)
+    plan.close()
+    # a plan without edge values refuses a message that needs them
+    plan2 = api.Plan(dev(indx, cuda_device), dev(rowptr, cuda_device)[:-1], dev(rowptr, cuda_device)[1:])
+    z = np.zeros((m, k), np.float32)
+    assert plan2.csr(M.MSG_SPMM, n, k, x, k, y, k, 0.0, z, k) == M.ERR_ARG
+    assert plan2.csr(M.MSG_GCN, n, k, x, k, y, k, 0.0, z, k) == 0
+    want = np.zeros((m, k), np.float32)
+    oracle.csr(M.MSG_GCN, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k)
+    assert rel_err(z, want) <= 1e-4
+
+
+def test_torch_custom_operator(cuda_device, oracle):
+    import torch
+    import fusedmm_b200.torch_op  # noqa: F401  (registers torch.ops.fusedmm_b200.csr)
+    rng = np.random.default_rng(17)
+    m, n, k = 1200, 900, 64
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 8, np.int64, np.int32, hub=1800)
+    rowptr = as_rowptr(pntrb, pntre)
+    val = val.astype(np.float32)
+    x, y = np.nan_to_num(dense(rng, m, k, k, np.float32)), np.nan_to_num(dense(rng, n, k, k, np.float32))
+    t = {nm: dev(a, cuda_device) for nm, a in dict(rp=rowptr, ix=indx, val=val, x=x, y=y).items()}
+    for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_SPMM, 0)):
+        want = np.zeros((m, k), np.float32)
+        oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop)
+        z = torch.ops.fusedmm_b200.csr(t["rp"], t["ix"], t["val"], t["x"], t["y"], msg, sop, 0.0, None)
+        s = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s):
+            z2 = torch.ops.fusedmm_b200.csr(t["rp"], t["ix"], t["val"], t["x"], t["y"], msg, sop, 0.0, None)
+        s.synchronize()
+        assert rel_err(z.cpu().numpy(), want) <= 1e-4 and torch.equal(z, z2)
+    with pytest.raises(Exception):
+        torch.ops.fusedmm_b200.csr(t["rp"], t["ix"], t["val"], t["x"], t["y"], 0x11F18, 0, 0.0, None)  # unknown VOP
