@@ -181,6 +181,27 @@ def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n,
            "note": "per rank: its CSR rows' pointers, all column ids, X rows and all of Y in; its Z rows out"}
     e2e_ok = bool(torch.isfinite(hz).all())
 
+    # the same with the graph kept on the device by a plan (inspector/executor split): per step only X(=Y) goes
+    # in and Z comes out; reported beside the headline figure, which stays the plain fusedMM_csr call
+    plan = api.Plan(hi, hpb[r0:], hpe[r0:], hv)
+    hz2 = torch.zeros((r1 - r0, k), dtype=tdtype).pin_memory()
+
+    def plan_step():
+        st = plan.csr(msg, n, k, hx[r0:], k, hx, k, 0.0, hz2, k, sop=sop if sop is not None else 0)
+        assert st == 0, api.status_string(st)
+        return api.call_info()
+
+    pinfo = plan_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        pinfo = plan_step()
+    barrier()
+    plan_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    plan.close()
+    e2e["with_plan"] = {"value": flops_per_edge * nnz / (plan_ms * 1e-3) * 1e-9, "ms_per_step": plan_ms,
+                        "h2d_bytes_per_step": int(pinfo.h2d_bytes), "d2h_bytes_per_step": int(pinfo.d2h_bytes),
+                        "same_z": bool(torch.equal(hz, hz2))}
     return e2e, e2e_ok
 
 
