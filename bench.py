@@ -183,7 +183,7 @@ def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n,
 
     # the same with the graph kept on the device by a plan (inspector/executor split): per step only X(=Y) goes
     # in and Z comes out; reported beside the headline figure, which stays the plain fusedMM_csr call
-    plan = api.Plan(hi, hpb[r0:], hpe[r0:], hv)
+    plan = api.Plan(hi, hpb[r0:r1], hpe[r0:r1], hv)  # this rank's rows
     hz2 = torch.zeros((r1 - r0, k), dtype=tdtype).pin_memory()
 
     def plan_step():
@@ -267,10 +267,14 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
+    saved_stdout = None
     if world > 1:
         import torch.distributed as dist
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"  # NCCL's version banner goes to stdout, which carries the JSON line
+        # NCCL writes its version banner straight to file descriptor 1 when the first communicator comes up;
+        # stdout carries the JSON line, so descriptor 1 points at stderr until that line is printed
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
     api.lib()
 
@@ -447,7 +451,11 @@ def main():
                "effective_gbs": synth.algorithmic_bytes(msg, nnz, n, k, es, 4, 8) / (ms_step * 1e-3) * 1e-9,
                "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks.summary(),
                "gpu_launches": launches_per_step * args.steps, "finite": finite and e2e_ok}
+        sys.stdout.flush()
+        if saved_stdout is not None:
+            os.dup2(saved_stdout, 1)
         print(json.dumps(out))
+        sys.stdout.flush()
     if world > 1:
         # leave without tearing down NCCL and the symmetric-memory mappings rank by rank: every rank has
         # passed the barrier, nothing is in flight, and a plain exit avoids teardown-order hangs
