@@ -729,7 +729,6 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       }
    }
    const long long rows_per_warp = vec_ok ? 32 / G : 1;  // short rows: one per group of G lanes
-   const long long row_grid = (a.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
    const long long hub_grid = static_cast<long long>(c.sm_count) * 8;
 
    // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
