@@ -32,6 +32,7 @@ import numpy as np  # noqa: E402
 
 DEFAULT_WORKLOAD = "c2_fr_rmat20_k256"
 METRIC = "fusedMM_csr GFLOP/s"
+L2_BYTES = 126 * 1000 * 1000
 
 
 def load_peaks():
@@ -347,14 +348,31 @@ def main():
     assert status == 0, api.status_string(status)
     uuid = torch.cuda.get_device_properties(dev).uuid
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # a workload whose Y fits in L2 would be timed warm: write a buffer larger than L2 before every timed
+    # step and time each step with its own pair of events (the flush stays outside the pairs)
+    flush = None
+    if n * k * es < 2 * L2_BYTES:
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+        config["l2"] = "inputs fit in the 126 MB L2: a 252 MB buffer is written before every timed step (outside the timed spans)"
     with ClockSampler(uuid) as clocks:
         barrier()
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        barrier()
-        ms_total = e0.elapsed_time(e1)
+        if flush is None:
+            e0.record()
+            for _ in range(args.steps):
+                step()
+            e1.record()
+            barrier()
+            ms_total = e0.elapsed_time(e1)
+        else:
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                     for _ in range(args.steps)]
+            for a, b in pairs:
+                flush.fill_(1)
+                a.record()
+                step()
+                b.record()
+            barrier()
+            ms_total = sum(a.elapsed_time(b) for a, b in pairs)
         # keep the sampler alive over a few more steps when the timed region was very short
         t_end = time.time() + max(0.0, 0.25 - ms_total * 1e-3)
         while time.time() < t_end:
@@ -385,6 +403,9 @@ def main():
     kms = {"scan": [], "rows": [], "chunks": [], "fixup": [], "main": []}
     launches_per_step = 0
     for _ in range(5):
+        if flush is not None:
+            flush.fill_(2)
+            torch.cuda.synchronize()
         st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all[r0:], pe_all[r0:], x[r0:],
                              k, x, k, 0.0, z[r0:], k, sop=sop if sop is not None else 0)
         assert st == 0

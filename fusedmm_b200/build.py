@@ -34,6 +34,7 @@ def _newer(target: Path, deps) -> bool:
 
 def build(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
     """Compile what is out of date and link.  Returns the path of the shared library."""
+    extra_flags = tuple(extra_flags) + tuple(os.environ.get("FUSEDMM_B200_NVCC_FLAGS", "").split())
     headers = sorted(CSRC.glob("*.cuh")) + sorted((PKG.parent / "include").glob("*.h"))
     sources = sorted(CSRC.glob("*.cu"))
     OBJDIR.mkdir(parents=True, exist_ok=True)

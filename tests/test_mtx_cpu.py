@@ -34,3 +34,11 @@ def test_pattern_symmetric_file_and_errors(tmp_path):
     short.write_text("%%MatrixMarket matrix coordinate real general\n3 3 2\n1 2 1.0\n")
     with pytest.raises(ValueError):
         read_mtx(short)
+
+
+def test_mtx_run_command_line_matches_the_reference_tester_flags():
+    from fusedmm_b200 import mtx_run
+    a = mtx_run.parse_args(["-input", "g.mtx", "-K", "64", "-nrep", "3", "-skHd", "1", "-t", "s", "-C", "1024"])
+    assert (a.input, a.K, a.nrep, a.skHd, a.t, a.T) == ("g.mtx", 64, 3, 1, "s", 0)
+    assert mtx_run.HEADER.split(",")[:5] == ["Filename", "NNZ", "M", "N", "K"]
+    assert set(mtx_run.KERNELS) == {"s", "t", "f", "m", "g"}

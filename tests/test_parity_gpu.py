@@ -726,3 +726,26 @@ def test_torch_custom_operator(cuda_device, oracle):
         assert rel_err(z.cpu().numpy(), want) <= 1e-4 and torch.equal(z, z2)
     with pytest.raises(Exception):
         torch.ops.fusedmm_b200.csr(t["rp"], t["ix"], t["val"], t["x"], t["y"], 0x11F18, 0, 0.0, None)  # unknown VOP
+
+
+def test_mtx_run_prints_the_testers_csv_line(cuda_device, tmp_path, capsys):
+    import io
+    from fusedmm_b200 import mtx_run
+    rng = np.random.default_rng(23)
+    n, e = 3000, 20000
+    r, c = rng.integers(1, n + 1, e), rng.integers(1, n + 1, e)
+    r[:4000] = 7                                               # one heavy row, so rows get split
+    path = tmp_path / "g.mtx"
+    with open(path, "w") as f:
+        f.write("%%MatrixMarket matrix coordinate pattern general\n%d %d %d\n" % (n, n, e))
+        f.writelines("%d %d\n" % (a, b) for a, b in zip(r, c))
+    for kern in "stfmg":
+        out = io.StringIO()
+        t0, t1 = mtx_run.run(mtx_run.parse_args(["-input", str(path), "-K", "48", "-nrep", "2", "-T", "1", "-t", kern]),
+                             out=out)
+        head, line = out.getvalue().strip().split("\n")
+        assert head == mtx_run.HEADER
+        fields = line.split(",")
+        assert fields[0] == str(path) and int(fields[2]) == n and int(fields[4]) == 48 and int(fields[1]) > e
+        assert t0 > 0 and t1 > 0 and abs(float(fields[7]) - t0 / t1) < 1e-3 * t0 / t1 + 1e-6
+        assert "PASSED TEST" in capsys.readouterr().err
