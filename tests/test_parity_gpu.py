@@ -737,7 +737,7 @@ def test_mtx_run_prints_the_testers_csv_line(cuda_device, tmp_path, capsys):
     r[:4000] = 7                                               # one heavy row, so rows get split
     path = tmp_path / "g.mtx"
     with open(path, "w") as f:
-        f.write("%%MatrixMarket matrix coordinate pattern general\n%d %d %d\n" % (n, n, e))
+        f.write("%%%%MatrixMarket matrix coordinate pattern general\n%d %d %d\n" % (n, n, e))
         f.writelines("%d %d\n" % (a, b) for a, b in zip(r, c))
     for kern in "stfmg":
         out = io.StringIO()
