@@ -162,6 +162,9 @@ struct DeviceCtx {
    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
    cudaEvent_t evk[4] = {nullptr, nullptr, nullptr, nullptr};  // after scan / rows; start and end of the chunk launch
    cudaStream_t side = nullptr;                 // the chunk and fix-up launches run beside the whole-row launch
+   // the same at the device's greatest stream priority (option side_priority, the default): when both launches are
+   // pending the block scheduler then places the chunk CTAs of split rows first, which measured 3-8 % faster
+   cudaStream_t side_hi = nullptr;
    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_side_end = nullptr;
    cudaStream_t copy = nullptr;                 // copies finished blocks of Z back to the host while later blocks compute
    cudaEvent_t ev_block[8] = {};
@@ -182,7 +185,7 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 512, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
-           engine = 0, edge_quantum = 256, stream_depth = 16;
+           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 8;
 };
 
 std::mutex g_mu;
@@ -239,6 +242,11 @@ int get_ctx(DeviceCtx **out)
       CK(cudaEventCreate(&c.ev1));
       for (auto &e : c.evk) CK(cudaEventCreate(&e));
       CK(cudaStreamCreateWithFlags(&c.side, cudaStreamNonBlocking));
+      {
+         int least = 0, greatest = 0;
+         CK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+         CK(cudaStreamCreateWithPriority(&c.side_hi, cudaStreamNonBlocking, greatest));
+      }
       CK(cudaEventCreateWithFlags(&c.ev_fork, cudaEventDisableTiming));
       CK(cudaEventCreateWithFlags(&c.ev_join, cudaEventDisableTiming));
       CK(cudaEventCreate(&c.ev_side_end));
@@ -729,7 +737,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       }
    }
    const long long rows_per_warp = vec_ok ? 32 / G : 1;  // short rows: one per group of G lanes
-   const long long hub_grid = static_cast<long long>(c.sm_count) * 8;
+   const long long hub_grid = static_cast<long long>(c.sm_count) * g_opt.chunk_ctas_per_sm;
 
    // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
    // (and their fix-up) on the side stream beside the whole rows on `st`, forked after the scan and joined
@@ -744,22 +752,26 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       }
       if (timing) CK(cudaEventRecord(c.evk[0], st));
       CK(cudaEventRecord(c.ev_fork, st));
-      CK(cudaStreamWaitEvent(c.side, c.ev_fork, 0));
-      if (timing) CK(cudaEventRecord(c.evk[2], c.side));
-      q.mode = MODE_HUB_CHUNKS;
-      if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, q, hub_grid, c.side)) return FUSEDMM_B200_ERR_ARG; }
-      else launch_any<T>(q, WARPS_PER_CTA, hub_grid, c.side);
-      if (timing) CK(cudaEventRecord(c.evk[3], c.side));
-      launch_fixup<T>(q, c.sm_count, c.side);
-      if (timing) CK(cudaEventRecord(c.ev_side_end, c.side));
-      CK(cudaEventRecord(c.ev_join, c.side));
-      launches += 2;
-      if (with_rows) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
+      cudaStream_t side = g_opt.side_priority ? c.side_hi : c.side;
+      auto rows_launch = [&]() -> int {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
+         if (!with_rows) return 0;
          q.mode = MODE_ROWS;
          if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, warps, q, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
          else launch_any<T>(q, warps, qgrid, st);
          launches++;
-      }
+         return 0;
+      };
+      CK(cudaStreamWaitEvent(side, c.ev_fork, 0));
+      if (timing) CK(cudaEventRecord(c.evk[2], side));
+      q.mode = MODE_HUB_CHUNKS;
+      if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, q, hub_grid, side)) return FUSEDMM_B200_ERR_ARG; }
+      else launch_any<T>(q, WARPS_PER_CTA, hub_grid, side);
+      if (timing) CK(cudaEventRecord(c.evk[3], side));
+      launch_fixup<T>(q, c.sm_count, side);
+      if (timing) CK(cudaEventRecord(c.ev_side_end, side));
+      CK(cudaEventRecord(c.ev_join, side));
+      launches += 2;
+      if (int e = rows_launch()) return e;
       if (timing) CK(cudaEventRecord(c.evk[1], st));
       CK(cudaStreamWaitEvent(st, c.ev_join, 0));
       CK(cudaGetLastError());
@@ -1473,6 +1485,8 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "engine")) return &g_opt.engine;
    if (!strcmp(name, "edge_quantum")) return &g_opt.edge_quantum;
    if (!strcmp(name, "stream_depth")) return &g_opt.stream_depth;
+   if (!strcmp(name, "side_priority")) return &g_opt.side_priority;
+   if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
 }
@@ -1481,10 +1495,11 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    std::lock_guard<std::mutex> lock(g_mu);
    int64_t *s = option_slot(name);
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic || s == &g_opt.side_priority) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.engine && value > 2) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.chunk_ctas_per_sm && (value < 1 || value > 64)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.edge_quantum && (value < 32 || value > (1ll << 24))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.stream_depth && (value < 1 || value > 32)) return FUSEDMM_B200_ERR_ARG;
    *s = value;
