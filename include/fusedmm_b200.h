@@ -218,8 +218,9 @@ int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, in
  *   - every array must already be in device memory (FUSEDMM_B200_ERR_ARG otherwise);
  *   - nnz must be the true number of edges of the m rows: it is what bounds the scratch. The call is
  *     refused with FUSEDMM_B200_ERR_LIMIT and a message on stderr when
- *     nnz/hub_chunk + 1 > 32768 (split rows) or 2*(nnz/hub_chunk) + 1 partial rows of k values do not
- *     fit in the array, e.g. more than about 16.4 million edges at k = 128 floats (hub_chunk = 512);
+ *     nnz/c + 1 > 32768 (split rows) or 2*(nnz/c) + 1 partial rows of k values do not fit in the
+ *     array, c = max(512, option hub_chunk) being the edges per piece this entry point uses, e.g. more
+ *     than about 16.4 million edges at k = 128 floats;
  *   - all launches go to `stream`, or to the legacy default stream when stream is NULL, in which case
  *     the call returns after they have finished;
  *   - the first call on a device looks up the array's address on that device; make that first call
@@ -300,7 +301,9 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *   "accept_vop_noop" 0 (default): VOP_NOOP returns status 2 as in the reference (fusedMM.c:346-377);
  *                    1: VOP_NOOP means T = Y_v.
  *   "hub_chunk"      most edges a row may have before it is split across warps, and edges per piece
- *                    (default 512; a call whose nnz argument says the graph is small uses less, down to 128).
+ *                    (default 256; a call whose nnz argument is below 2^24 uses at most 128 unless a row
+ *                    of k values exceeds 1024 bytes).
+ *   "chunk_ctas_per_sm"  blocks per SM of the launch that works on the pieces of split rows (default 3).
  *   "force_tiling"   0 = automatic; otherwise (register_budget << 24) | (gathers_in_flight << 16) |
  *                    (lanes_per_edge << 8) | vectors_per_lane; gathers_in_flight 0 means that tiling's
  *                    default, register_budget 0 the compiler's choice (only instantiated combinations

@@ -95,9 +95,9 @@ def test_status_codes_of_invalid_messages(lib):
 
 
 def test_options_and_sop_registry(lib):
-    assert api.get_option("hub_chunk") == 512
+    assert api.get_option("hub_chunk") == 256
     assert api.set_option("hub_chunk", 64) == 0 and api.get_option("hub_chunk") == 64
-    assert api.set_option("hub_chunk", 512) == 0
+    assert api.set_option("hub_chunk", 256) == 0
     assert api.set_option("hub_chunk", 3) == M.ERR_ARG
     assert api.set_option("no_such_option", 1) == M.ERR_ARG
     assert api.set_option("accept_vop_noop", 1) == 0

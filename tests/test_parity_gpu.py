@@ -322,7 +322,7 @@ def test_scratch_grows_when_there_are_many_split_rows(cuda_device, oracle):
         st, z = run_gpu(cuda_device, M.MSG_SPMM, m, n, k, val, indx, pntrb, pntre, None, k, y, k, 1.0, z0, k)
         info = api.call_info()
     finally:
-        api.set_option("hub_chunk", 512)
+        api.set_option("hub_chunk", 256)
     assert st == 0 and info.hub_rows == m and info.hub_chunks == 2 * m
     want = np.ones((m, k), np.float32)
     oracle.csr(M.MSG_SPMM, m, n, k, val, indx, pntrb, pntre, y, k, y, k, 1.0, want, k)
