@@ -185,7 +185,7 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
-           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3;
+           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1;
 };
 
 std::mutex g_mu;
@@ -748,7 +748,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       }
       if (timing) CK(cudaEventRecord(c.evk[0], st));
       CK(cudaEventRecord(c.ev_fork, st));
-      cudaStream_t side = g_opt.side_priority ? c.side_hi : c.side;
+      cudaStream_t side = !g_opt.side_stream ? st : (g_opt.side_priority ? c.side_hi : c.side);
       auto rows_launch = [&]() -> int {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
          if (!with_rows) return 0;
          q.mode = MODE_ROWS;
@@ -1477,6 +1477,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "edge_quantum")) return &g_opt.edge_quantum;
    if (!strcmp(name, "stream_depth")) return &g_opt.stream_depth;
    if (!strcmp(name, "side_priority")) return &g_opt.side_priority;
+   if (!strcmp(name, "side_stream")) return &g_opt.side_stream;
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
