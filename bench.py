@@ -305,7 +305,7 @@ def main():
                 pz = fdist.PeerZ(n, k, tdtype, dev, dist)
                 z = pz.z
                 z.zero_()
-                if pz.multicast and os.environ.get("FUSEDMM_BENCH_MULTICAST", "1") == "1":
+                if os.environ.get("FUSEDMM_BENCH_MULTICAST", "1" if pz.use_multicast() else "0") == "1" and pz.multicast:
                     exchange = ("fused: kernels store each finished row once through the NVSwitch multicast mapping of Z "
                                 "(multimem.st), one small all-reduce orders the ranks")
                 else:

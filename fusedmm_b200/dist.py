@@ -76,6 +76,13 @@ class PeerZ:
         """Multicast address of row ``r0`` (None without NVSwitch multicast)."""
         return self.multicast + r0 * self.row_bytes if self.multicast else None
 
+    def use_multicast(self):
+        """Multicast stores pay from three GPUs on: every GPU then receives all of Z once whatever the number
+        of ranks, while per-peer stores make the rank with the most rows send them N-1 times.  Between two GPUs
+        a multicast store also loops this rank's own rows back through the switch, and plain peer stores measured
+        7 % faster."""
+        return bool(self.multicast) and self.world > 2
+
     def finish_step(self):
         """Enqueue the collective that follows this rank's kernels in stream order; when it completes on a
         rank, every rank's kernels of the step (and with them their stores into this rank's Z) are done."""
@@ -92,7 +99,7 @@ def fusedMM_csr_fused_exchange(imessage, n, k, val, indx, rowptr, x, y, pz: Peer
     if r1 > r0:
         st = api.fusedMM_csr(imessage, r1 - r0, n, k, 1.0, int(indx.numel()), n, n, val, indx, rowptr[r0:-1],
                              rowptr[r0 + 1:], x[r0:], k, y, k, 0.0, pz.z[r0:], k, sop=sop, stream=stream,
-                             z_peers=None if pz.multicast else pz.peers_at_row(r0),
-                             z_multicast=pz.multicast_at_row(r0))
+                             z_peers=None if pz.use_multicast() else pz.peers_at_row(r0),
+                             z_multicast=pz.multicast_at_row(r0) if pz.use_multicast() else None)
     pz.finish_step()
     return st
