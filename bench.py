@@ -283,7 +283,10 @@ def main():
     n, k, nnz, msg, sop = cfg["n"], cfg["k"], csr.nnz, cfg["msg"], cfg["sop"]
     pb_all, pe_all = csr.pntrb.contiguous(), csr.pntre.contiguous()
     rowptr_host = csr.rowptr.cpu().numpy()
-    bounds = api.shard_rows(rowptr_host[:-1].copy(), rowptr_host[1:].copy(), world)
+    bounds = api.shard_rows(rowptr_host[:-1].copy(), rowptr_host[1:].copy(), world,
+                            row_weight=int(os.environ.get("FUSEDMM_BENCH_ROW_WEIGHT", "8")))
+    if world > 1:
+        config["row_shard_cost"] = "edges + %s per row" % os.environ.get("FUSEDMM_BENCH_ROW_WEIGHT", "8")
     r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
     my_edges = int(rowptr_host[r1] - rowptr_host[r0])
     z = torch.zeros((n, k), dtype=tdtype, device=dev)

@@ -186,16 +186,17 @@ def gfusedMM_csr(tkern, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pntre
        ptrs[1], ptrs[2], ptrs[3], ptrs[4], lda, ptrs[5], ldb, beta, ptrs[6], ldc)
 
 
-def shard_rows(pntrb, pntre, nshards):
-    """nnz-balanced contiguous row ranges (``fusedmm_b200_shard_rows_*``); host NumPy row pointers."""
+def shard_rows(pntrb, pntre, nshards, row_weight=0):
+    """Contiguous row ranges of equal cost, a row costing its edges plus ``row_weight``
+    (``fusedmm_b200_shard_rows_weighted_*``; 0 = balanced by edges alone); host NumPy row pointers."""
     L = lib()
     pntrb = np.ascontiguousarray(pntrb)
     pntre = np.ascontiguousarray(pntre)
     m = len(pntrb)
     bounds = np.zeros(nshards + 1, dtype=np.int64)
-    fn = L.fusedmm_b200_shard_rows_i32 if pntrb.dtype == np.int32 else L.fusedmm_b200_shard_rows_i64
-    fn.argtypes = [C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
-    st = fn(m, nshards, pntrb.ctypes.data, pntre.ctypes.data, bounds.ctypes.data)
+    fn = L.fusedmm_b200_shard_rows_weighted_i32 if pntrb.dtype == np.int32 else L.fusedmm_b200_shard_rows_weighted_i64
+    fn.argtypes = [C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    st = fn(m, nshards, pntrb.ctypes.data, pntre.ctypes.data, int(row_weight), bounds.ctypes.data)
     if st:
         raise FusedMMError(status_string(st))
     return bounds

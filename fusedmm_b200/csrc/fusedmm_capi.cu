@@ -456,7 +456,7 @@ long long max_entry(const PT *a, long long m)
 
 constexpr int PIPE_BLOCKS = 8;  // row blocks of the copy-back pipeline (one counter word and one event each)
 template <typename PT>
-int shard_rows(int64_t m, int32_t nshards, const PT *pntrb, const PT *pntre, int64_t *bounds);
+int shard_rows(int64_t m, int32_t nshards, const PT *pntrb, const PT *pntre, int64_t *bounds, int64_t row_weight = 0);
 
 template <typename T>
 int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b200_sop &sopk,
@@ -1127,12 +1127,13 @@ int32_t letter_to_message(char tkern)
 }
 
 template <typename PT>
-int shard_rows(int64_t m, int32_t nshards, const PT *pntrb, const PT *pntre, int64_t *bounds)
+int shard_rows(int64_t m, int32_t nshards, const PT *pntrb, const PT *pntre, int64_t *bounds, int64_t row_weight)
 {
-   if (m < 0 || nshards < 1 || !bounds || (m > 0 && (!pntrb || !pntre))) return FUSEDMM_B200_ERR_ARG;
-   // prefix of edge counts, then the first row whose prefix reaches g/nshards of the total
+   if (m < 0 || nshards < 1 || row_weight < 0 || !bounds || (m > 0 && (!pntrb || !pntre))) return FUSEDMM_B200_ERR_ARG;
+   // prefix of the rows' costs (edges + row_weight each), then the first row whose prefix reaches g/nshards of the total
    std::vector<int64_t> pre(m + 1, 0);
-   for (int64_t i = 0; i < m; i++) pre[i + 1] = pre[i] + std::max<int64_t>(0, static_cast<int64_t>(pntre[i]) - static_cast<int64_t>(pntrb[i]));
+   for (int64_t i = 0; i < m; i++)
+      pre[i + 1] = pre[i] + row_weight + std::max<int64_t>(0, static_cast<int64_t>(pntre[i]) - static_cast<int64_t>(pntrb[i]));
    const int64_t total = pre[m];
    bounds[0] = 0;
    for (int32_t g = 1; g < nshards; g++) {
@@ -1462,6 +1463,16 @@ int fusedmm_b200_shard_rows_i32(int64_t m, int32_t nshards, const int32_t *pntrb
 int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb, const int64_t *pntre, int64_t *bounds)
 {
    return shard_rows(m, nshards, pntrb, pntre, bounds);
+}
+int fusedmm_b200_shard_rows_weighted_i32(int64_t m, int32_t nshards, const int32_t *pntrb, const int32_t *pntre, int64_t row_weight,
+                                         int64_t *bounds)
+{
+   return shard_rows(m, nshards, pntrb, pntre, bounds, row_weight);
+}
+int fusedmm_b200_shard_rows_weighted_i64(int64_t m, int32_t nshards, const int64_t *pntrb, const int64_t *pntre, int64_t row_weight,
+                                         int64_t *bounds)
+{
+   return shard_rows(m, nshards, pntrb, pntre, bounds, row_weight);
 }
 
 static int64_t *option_slot(const char *name)

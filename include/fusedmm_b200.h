@@ -278,6 +278,13 @@ int fusedmm_b200_shard_rows_i32(int64_t m, int32_t nshards, const int32_t *pntrb
                                 const int32_t *pntre, int64_t *bounds);
 int fusedmm_b200_shard_rows_i64(int64_t m, int32_t nshards, const int64_t *pntrb,
                                 const int64_t *pntre, int64_t *bounds);
+/* The same with a fixed cost per row added to its edge count (row_weight >= 0, in edges): a row also costs a
+ * read of X_u, a write of Z_u and, between GPUs, the transfer of Z_u, whatever its degree.  0 gives the
+ * functions above. */
+int fusedmm_b200_shard_rows_weighted_i32(int64_t m, int32_t nshards, const int32_t *pntrb,
+                                         const int32_t *pntre, int64_t row_weight, int64_t *bounds);
+int fusedmm_b200_shard_rows_weighted_i64(int64_t m, int32_t nshards, const int64_t *pntrb,
+                                         const int64_t *pntre, int64_t row_weight, int64_t *bounds);
 
 /* ------------------------------------------------------------------------------------------------
  * Validates a CSR on the GPU before it is trusted (the kernels themselves do not bounds-check, like

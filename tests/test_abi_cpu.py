@@ -128,3 +128,21 @@ def test_shard_rows_balances_edges(lib, dt):
     assert (b == 0).all()
     b = api.shard_rows(np.zeros(10, dt), np.zeros(10, dt), 4)  # no edges at all
     assert b[0] == 0 and b[-1] == 10 and (np.diff(b) >= 0).all()
+
+
+def test_shard_rows_with_a_row_weight_balances_rows_plus_edges(lib):
+    rng = np.random.default_rng(1)
+    deg = rng.poisson(3, size=6000)
+    deg[:50] = 2000  # the heavy rows come first, as in an R-MAT graph
+    rowptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    plain = api.shard_rows(rowptr[:-1], rowptr[1:], 2)
+    assert (plain == api.shard_rows(rowptr[:-1], rowptr[1:], 2, row_weight=0)).all()
+    w = 40
+    b = api.shard_rows(rowptr[:-1], rowptr[1:], 2, row_weight=w)
+    cost = [int(rowptr[b[i + 1]] - rowptr[b[i]]) + w * int(b[i + 1] - b[i]) for i in range(2)]
+    assert abs(cost[0] - cost[1]) <= 2000 + w and b[1] > plain[1]  # the first shard takes more of the light rows
+    with pytest.raises(api.FusedMMError):
+        api.shard_rows(rowptr[:-1], rowptr[1:], 2, row_weight=-1)
+    # no edges at all: rows alone are balanced
+    b = api.shard_rows(np.zeros(10, np.int32), np.zeros(10, np.int32), 5, row_weight=1)
+    assert list(b) == [0, 2, 4, 6, 8, 10]
