@@ -185,7 +185,7 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
-           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1;
+           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0;
 };
 
 std::mutex g_mu;
@@ -639,6 +639,16 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       } else choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
+   // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
+   int Gr = G, NVr = NV, Ur = U;
+   if (vec_ok && g_opt.force_tiling_rows) {
+      Gr = static_cast<int>((g_opt.force_tiling_rows >> 8) & 0xFF);
+      NVr = static_cast<int>(g_opt.force_tiling_rows & 0xFF);
+      Ur = static_cast<int>((g_opt.force_tiling_rows >> 16) & 0xFF);
+      if (Ur == 0) Ur = default_u(Gr, NVr);
+      Ur |= static_cast<int>((g_opt.force_tiling_rows >> 24) & 0xFF) << 8;
+      if (Gr == 0 || 32 % Gr != 0 || static_cast<long long>(Gr) * NVr * W < a.k) return FUSEDMM_B200_ERR_ARG;
+   }
    const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
 
    int launches = 0;
@@ -732,7 +742,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          }
       }
    }
-   const long long rows_per_warp = vec_ok ? 32 / G : 1;  // short rows: one per group of G lanes
+   const long long rows_per_warp = vec_ok ? 32 / Gr : 1;  // short rows: one per group of lanes
    const long long hub_grid = static_cast<long long>(c.sm_count) * g_opt.chunk_ctas_per_sm;
 
    // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
@@ -752,7 +762,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       auto rows_launch = [&]() -> int {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
          if (!with_rows) return 0;
          q.mode = MODE_ROWS;
-         if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, warps, q, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
+         if (vec_ok) { if (!launch_vec<T>(pattern, Gr, NVr, Ur, warps, q, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
          else launch_any<T>(q, warps, qgrid, st);
          launches++;
          return 0;
@@ -1489,6 +1499,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "stream_depth")) return &g_opt.stream_depth;
    if (!strcmp(name, "side_priority")) return &g_opt.side_priority;
    if (!strcmp(name, "side_stream")) return &g_opt.side_stream;
+   if (!strcmp(name, "force_tiling_rows")) return &g_opt.force_tiling_rows;
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;

@@ -326,6 +326,9 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *   "side_priority"  1 (default): the stream that carries the chunks of split rows has the device's greatest
  *                    priority, so their blocks are placed before the whole-row launch's when both are pending
  *                    (3-8 % faster on a B200); 0: default priority.
+ *   "side_stream"    1 (default): the chunks of split rows run on a second stream beside the whole rows;
+ *                    0: every launch on one stream (12 % slower on the benchmark graph; diagnostic).
+ *   "force_tiling_rows"  as force_tiling, for the whole-row launch only (0 = the call's tiling).
  *   "force_generic"  1 = run every message through the flag-interpreting kernel.
  *   "inject_alloc_failure"  n > 0: the n-th device allocation the library attempts from now on fails
  *                    with FUSEDMM_B200_ERR_NOMEM (host-side fault injection for tests; nothing is
