@@ -84,8 +84,9 @@ def one_case(rng, device, oracle, case):
     return 0, 0, 0
 
 
-def test_fuzz_against_the_oracle(cuda_device, oracle):
-    rng = np.random.default_rng(20240607)
+@pytest.mark.parametrize("seed", [20240607, 7, 99])
+def test_fuzz_against_the_oracle(cuda_device, oracle, seed):
+    rng = np.random.default_rng(seed)
     compared = stream = strided = 0
     for case in range(1500):
         c, s, a = one_case(rng, cuda_device, oracle, case)
