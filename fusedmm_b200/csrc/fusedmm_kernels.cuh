@@ -216,6 +216,55 @@ __device__ __forceinline__ T aop_identity(int aop)
    return aop == AOP_MAX ? -pos_inf<T>() : (aop == AOP_MIN ? pos_inf<T>() : T(0));
 }
 
+// The same stage bodies over a lane's whole share of an edge, with the switch OUTSIDE the element loops: the
+// flag-interpreting instantiation then pays one uniform branch per stage and edge instead of one per element.
+#define FMM_FOR_VI _Pragma("unroll") for (int v = 0; v < NV; v++) _Pragma("unroll") for (int i = 0; i < W; i++)
+template <typename T, int NV, int W>
+__device__ __forceinline__ void vop_block(int vop, const T (&x)[NV][W], T (&y)[NV][W])
+{
+   switch (vop) {
+      case VOP_COPY_LHS: FMM_FOR_VI y[v][i] = x[v][i]; break;
+      case VOP_ADD:      FMM_FOR_VI y[v][i] = x[v][i] + y[v][i]; break;
+      case VOP_SUBL:     FMM_FOR_VI y[v][i] = y[v][i] - x[v][i]; break;
+      case VOP_SUBR:     FMM_FOR_VI y[v][i] = x[v][i] - y[v][i]; break;
+      case VOP_MAX:      FMM_FOR_VI y[v][i] = x[v][i] > y[v][i] ? x[v][i] : y[v][i]; break;
+      case VOP_MIN:      FMM_FOR_VI y[v][i] = x[v][i] < y[v][i] ? x[v][i] : y[v][i]; break;
+      default: break;  // VOP_COPY_RHS: T is the gathered row
+   }
+}
+// ps[i] += the reduction terms of this lane's elements, in the element order of rop_term's callers
+template <typename T, int NV, int W>
+__device__ __forceinline__ void rop_block(int rop, const T (&x)[NV][W], const T (&t)[NV][W], T (&ps)[W])
+{
+   switch (rop) {
+      case ROP_DOT:     FMM_FOR_VI ps[i] += x[v][i] * t[v][i]; break;
+      case ROP_ADD_LHS: FMM_FOR_VI ps[i] += x[v][i]; break;
+      case ROP_ADD_RHS: FMM_FOR_VI ps[i] += t[v][i]; break;
+      case ROP_NORML:   FMM_FOR_VI ps[i] += x[v][i] * x[v][i]; break;
+      case ROP_NORMR:   FMM_FOR_VI ps[i] += t[v][i] * t[v][i]; break;
+      default: break;   // ROP_NOOP
+   }
+}
+// acc = AOP(acc, VSC(out, t))
+template <typename T, int NV, int W>
+__device__ __forceinline__ void vsc_aop_block(int vsc, int aop, T out, const T (&t)[NV][W], T (&acc)[NV][W])
+{
+   const int a = aop == AOP_MAX ? 1 : (aop == AOP_MIN ? 2 : 0);
+   const int m = vsc == VSC_MUL ? 1 : (vsc == VSC_ADD ? 2 : 0);
+   switch (m * 3 + a) {
+      case 0: FMM_FOR_VI acc[v][i] += t[v][i]; break;
+      case 1: FMM_FOR_VI { const T tt = t[v][i]; acc[v][i] = acc[v][i] > tt ? acc[v][i] : tt; } break;
+      case 2: FMM_FOR_VI { const T tt = t[v][i]; acc[v][i] = acc[v][i] < tt ? acc[v][i] : tt; } break;
+      case 3: FMM_FOR_VI acc[v][i] += out * t[v][i]; break;
+      case 4: FMM_FOR_VI { const T tt = out * t[v][i]; acc[v][i] = acc[v][i] > tt ? acc[v][i] : tt; } break;
+      case 5: FMM_FOR_VI { const T tt = out * t[v][i]; acc[v][i] = acc[v][i] < tt ? acc[v][i] : tt; } break;
+      case 6: FMM_FOR_VI acc[v][i] += out + t[v][i]; break;
+      case 7: FMM_FOR_VI { const T tt = out + t[v][i]; acc[v][i] = acc[v][i] > tt ? acc[v][i] : tt; } break;
+      default: FMM_FOR_VI { const T tt = out + t[v][i]; acc[v][i] = acc[v][i] < tt ? acc[v][i] : tt; } break;
+   }
+}
+#undef FMM_FOR_VI
+
 // Scalar functions.  fp32 uses expf/logf-class functions (a few ulp), never the fast intrinsics; the
 // table variant computes its index in double exactly as the host code it mirrors
 // (test/fusedMMtime.cpp:606-611).
@@ -305,6 +354,8 @@ template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int
 struct VecEngine {
    static constexpr int W = VecOf<T>::W;
    static constexpr int S = 32 / G;  // edge slots per warp
+   // the flag-interpreting instantiation: stage codes are only known at run time
+   static constexpr bool RUNTIME_CODES = VOPC < 0 || ROPC < 0 || VSCC < 0 || AOPC < 0;
    static_assert(S * U <= 32 && (32 % (S * U)) == 0, "S*U must divide 32");
    static_assert(U <= G && (U & (U - 1)) == 0, "U must be a power of two no larger than G");
 
@@ -381,13 +432,18 @@ struct VecEngine {
                T ps[W];
 #pragma unroll
                for (int i = 0; i < W; i++) ps[i] = T(0);
+               if constexpr (RUNTIME_CODES) {
+                  vop_block<T, NV, W>(vop, xv, yv[u]);
+                  rop_block<T, NV, W>(rop, xv, yv[u], ps);
+               } else {
 #pragma unroll
-               for (int v = 0; v < NV; v++)
+                  for (int v = 0; v < NV; v++)
 #pragma unroll
-                  for (int i = 0; i < W; i++) {
-                     yv[u][v][i] = vop_apply(vop, xv[v][i], yv[u][v][i]);
-                     if (rop != ROP_NOOP) ps[i] += rop_term(rop, xv[v][i], yv[u][v][i]);
-                  }
+                     for (int i = 0; i < W; i++) {
+                        yv[u][v][i] = vop_apply(vop, xv[v][i], yv[u][v][i]);
+                        if (rop != ROP_NOOP) ps[i] += rop_term(rop, xv[v][i], yv[u][v][i]);
+                     }
+               }
                part[u] = ps[0];
 #pragma unroll
                for (int i = 1; i < W; i++) part[u] += ps[i];
@@ -418,15 +474,19 @@ struct VecEngine {
             for (int u = 0; u < U; u++) {
                const T out = __shfl_sync(FULL, out_mine, u * (G / U), G);
                if (ok[u]) {
+                  if constexpr (RUNTIME_CODES) {
+                     vsc_aop_block<T, NV, W>(vsc, aop, out, yv[u], acc);
+                  } else {
 #pragma unroll
-                  for (int v = 0; v < NV; v++)
+                     for (int v = 0; v < NV; v++)
 #pragma unroll
-                     for (int i = 0; i < W; i++) {
-                        T tt = yv[u][v][i];
-                        if (vsc == VSC_MUL) tt = out * tt;
-                        else if (vsc == VSC_ADD) tt = out + tt;
-                        acc[v][i] = aop_apply(aop, acc[v][i], tt);
-                     }
+                        for (int i = 0; i < W; i++) {
+                           T tt = yv[u][v][i];
+                           if (vsc == VSC_MUL) tt = out * tt;
+                           else if (vsc == VSC_ADD) tt = out + tt;
+                           acc[v][i] = aop_apply(aop, acc[v][i], tt);
+                        }
+                  }
                }
             }
          }
