@@ -636,7 +636,13 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          U = static_cast<int>((g_opt.force_tiling >> 16) & 0xFF);
          if (U == 0) U = default_u(G, NV);
          U |= static_cast<int>((g_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
-      } else choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
+      } else {
+         choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
+         // the 80-register budget of the (32, 4, 2) tiling was tuned on the specialised kernels; the flag-interpreting
+         // one needs more registers and loses with it (K = 512 SpMM message: 52.0 ms with the budget, 43.8 without),
+         // while the 64-register budget of (8, 2, 4) helps it too (K = 64: 3.48 ms against 4.46)
+         if ((g_opt.force_generic || d.pattern == PAT_GENERIC) && NV == 4) U &= 0xFF;
+      }
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
@@ -1081,6 +1087,7 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
    int G = 0, NV = 0, U = 0;
    if (vec_ok) {
       choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
+      if (d.pattern == PAT_GENERIC && NV == 4) U &= 0xFF;  // as in the allocating entry point
       if (G == 0) vec_ok = false;
    }
    const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
