@@ -424,6 +424,17 @@ void choose_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
    else if (nvec <= 256) { *G = 32; *NV = 8; *U = 1; }
    else { *G = 0; *NV = 0; *U = 0; }
 }
+// The flag-interpreting kernels need more registers than the specialised ones, so their best register budget and
+// number of gathers in flight differ (B200, float): K = 512 SpMM message 43.8 ms without the 80-register budget of
+// (32, 4, 2) against 52.0 with it; K = 256 FR message 7.24 ms with an 80-register budget on (32, 2, 4) against 8.95
+// without; K = 128 sigmoid message 22.8 ms with 4 gathers in flight on (16, 2) against 26.3 with 8; the 64-register
+// budget of (8, 2, 4) helps both kinds (K = 64: 3.48 ms against 4.46).
+void tiling_for_generic(int G, int NV, int *U)
+{
+   if (G == 32 && NV == 4) *U &= 0xFF;
+   else if (G == 32 && NV == 2 && *U == 4) *U = 4 | (3 << 8);
+   else if (G == 16 && NV == 2 && *U == 8) *U = 4;
+}
 // U of the default instantiation of a (G, NV) tiling
 int default_u(int G, int NV)
 {
@@ -638,10 +649,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          U |= static_cast<int>((g_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
       } else {
          choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
-         // the 80-register budget of the (32, 4, 2) tiling was tuned on the specialised kernels; the flag-interpreting
-         // one needs more registers and loses with it (K = 512 SpMM message: 52.0 ms with the budget, 43.8 without),
-         // while the 64-register budget of (8, 2, 4) helps it too (K = 64: 3.48 ms against 4.46)
-         if ((g_opt.force_generic || d.pattern == PAT_GENERIC) && NV == 4) U &= 0xFF;
+         if (g_opt.force_generic || d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
       }
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
@@ -1087,7 +1095,7 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
    int G = 0, NV = 0, U = 0;
    if (vec_ok) {
       choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
-      if (d.pattern == PAT_GENERIC && NV == 4) U &= 0xFF;  // as in the allocating entry point
+      if (d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
       if (G == 0) vec_ok = false;
    }
    const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));

@@ -13,6 +13,12 @@ namespace fmm {
    X(32, 1, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 0) X(32, 8, 1, 0) \
    X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3)
 
+// A translation unit may add tilings of its own by defining this before the include (the flag-interpreting
+// kernels need other register budgets than the specialised ones).
+#ifndef FMM_FOR_EACH_EXTRA_TILING
+#define FMM_FOR_EACH_EXTRA_TILING(X)
+#endif
+
 // Edge-stream scheduler: (G, NV).
 #define FMM_FOR_EACH_STREAM_TILING(X) \
    X(4, 1) X(8, 1) X(8, 2) X(8, 4) X(16, 1) X(16, 2) X(16, 4) X(32, 1) X(32, 2) X(32, 4) X(32, 8)
@@ -57,6 +63,7 @@ namespace fmm {
       U &= 0xFF;                                                                                      \
       switch ((MB << 24) | (U << 16) | (G << 8) | NV) {                                               \
          FMM_FOR_EACH_TILING(FMM_TILING_CASE)                                                         \
+         FMM_FOR_EACH_EXTRA_TILING(FMM_TILING_CASE)                                                   \
          default: return false;                                                                       \
       }                                                                                               \
    }
