@@ -25,7 +25,7 @@ struct fusedmm_b200_plan {
    void *own[4] = {nullptr, nullptr, nullptr, nullptr};  // device copies made from host arrays (val, indx, pntrb, pntre)
    const void *val = nullptr, *indx = nullptr, *pntrb = nullptr, *pntre = nullptr;  // device addresses used by the calls
    long long *hub_row = nullptr, *hub_base = nullptr;
-   unsigned long long *counter = nullptr;  // packed (split rows << 40) | chunks, written once by the scan
+   unsigned long long *counter = nullptr;  // packed (split rows << HUB_SHIFT) | chunks, written once by the scan
    long long nh = 0, nchunks = 0;
 };
 
@@ -185,7 +185,8 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
-           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0;
+           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
+           strict_udef = 0;
 };
 
 std::mutex g_mu;
@@ -320,7 +321,11 @@ bool close_enough(T a, T b)
 template <typename T>
 bool identify_udef(int (*hook)(T, T *), fusedmm_b200_sop *found)
 {
-   static const double pts[] = {-7.5, -3.0, -1.25, -0.5, -0.0625, 0.03125, 0.3, 0.75, 1.0, 1.7, 2.9, 4.2, 6.0, 11.0};
+   // inside and outside the table range of the tester's sigmoid (+-5), on both sides of its edges and of the
+   // clamp of its t-distribution scale, at 0 and at large magnitudes: a function that agrees with a built-in
+   // only on a middle range is not taken for it
+   static const double pts[] = {-1000.0, -30.0, -8.5, -7.5, -5.0625, -4.96875, -3.0, -1.25, -0.625, -0.5, -0.0625, 0.0,
+                                0.03125, 0.3, 0.75, 1.0, 1.7, 2.9, 4.2, 4.96875, 5.0625, 6.0, 11.0, 30.0, 1000.0};
    constexpr int NP = sizeof(pts) / sizeof(pts[0]);
    T got[NP];
    for (int i = 0; i < NP; i++) {
@@ -338,7 +343,7 @@ bool identify_udef(int (*hook)(T, T *), fusedmm_b200_sop *found)
       if (all) { *found = k; return true; }
    }
    // p0/(p1+s), optionally clamped to +-p2: solve from two points of the unclamped range
-   const int ia = 8, ib = 10;  // s = 1.0 and s = 2.9
+   const int ia = 15, ib = 17;  // s = 1.0 and s = 2.9
    const double oa = got[ia], ob = got[ib], sa = pts[ia], sb = pts[ib];
    if (std::isfinite(oa) && std::isfinite(ob) && oa != ob) {
       const double p1 = (ob * sb - oa * sa) / (oa - ob);
@@ -807,16 +812,16 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    };
 
    // ---- Z goes back to a host array: copy it block of rows by block of rows while later blocks compute ----
-   bool rows_done = false;
    if (a.plan) CKI(ensure_buf(c.partials, static_cast<size_t>(std::max<long long>(a.plan->nchunks, 1)) * a.k * es));
    if (!a.plan && !async && !on_dev[6] && !on_dev[2] && !on_dev[3] && static_cast<size_t>(a.m) * a.k * es >= (static_cast<size_t>(32) << 20)) {
       int64_t bounds[PIPE_BLOCKS + 1];
       CKI(a.ptr_bits == 64 ? shard_rows(a.m, PIPE_BLOCKS, static_cast<const int64_t *>(a.pntrb), static_cast<const int64_t *>(a.pntre), bounds)
                            : shard_rows(a.m, PIPE_BLOCKS, static_cast<const int32_t *>(a.pntrb), static_cast<const int32_t *>(a.pntre), bounds));
-      bind_scratch(p);
-      for (int b = 0; b < PIPE_BLOCKS; b++) {
+      // One block: its rows through the row scheduler (whole rows only on the first pass), then its part of Z back
+      // to the host on the copy stream while the next block computes.
+      auto run_block = [&](int b, bool with_rows) -> int {
          const long long r0 = bounds[b], r1 = bounds[b + 1];
-         if (r1 <= r0) continue;
+         if (r1 <= r0) return 0;
          Params<T> q = p;
          q.m = r1 - r0;
          q.pntrb = static_cast<const char *>(p.pntrb) + r0 * ps;
@@ -824,42 +829,58 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          if (q.x) q.x = p.x + r0 * p.ldx;
          q.z = p.z + r0 * p.ldz;
          q.counter = p.counter + 2 + b;  // words 0 and 1 belong to the unblocked passes
-         CKI(enqueue_pass(q, true, false));
+         CKI(enqueue_pass(q, with_rows, false));
          CK(cudaEventRecord(c.ev_block[b], st));
          CK(cudaStreamWaitEvent(c.copy, c.ev_block[b], 0));
          const char *src = static_cast<const char *>(c.stage[6].ptr) + static_cast<size_t>(r0) * a.k * es;
          char *dst = static_cast<char *>(a.z) + static_cast<size_t>(r0) * a.ldz * es;
          if (a.ldz == a.k) CK(cudaMemcpyAsync(dst, src, static_cast<size_t>(r1 - r0) * a.k * es, cudaMemcpyDeviceToHost, c.copy));
          else CK(cudaMemcpy2DAsync(dst, a.ldz * es, src, a.k * es, a.k * es, r1 - r0, cudaMemcpyDeviceToHost, c.copy));
-      }
-      unsigned long long words[PIPE_BLOCKS] = {};
-      CK(cudaMemcpyAsync(words, p.counter + 2, sizeof(words), cudaMemcpyDeviceToHost, st));
-      CK(cudaStreamSynchronize(st));
-      CK(cudaStreamSynchronize(c.copy));
-      rows_done = true;
-      bool fits = true;
-      for (int b = 0; b < PIPE_BLOCKS; b++) {
-         const long long bh = static_cast<long long>(words[b] >> HUB_SHIFT), bc = static_cast<long long>(words[b] & HUB_CHUNK_MASK);
-         fits = fits && bh <= p.hub_cap && bc <= p.chunk_cap;
-         nh += bh;
-         nchunks += bc;
-      }
-      if (fits) {
-         z_returned = true;
-         d2h += a.m * a.k * es;
-      } else {  // some block found the scratch too small: redo the split rows of all blocks below, then copy all of Z
-         c.hub_cap = std::max(c.hub_cap, nh + nh / 4 + 1024);
-         CKI(ensure_buf(c.hub_row, c.hub_cap * sizeof(long long)));
-         CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
-         CKI(ensure_buf(c.partials, static_cast<size_t>(nchunks + nchunks / 8 + 64) * a.k * es));
+         return 0;
+      };
+      bool redo[PIPE_BLOCKS];
+      for (int b = 0; b < PIPE_BLOCKS; b++) redo[b] = true;
+      for (int attempt = 0; attempt < 3; attempt++) {
+         bind_scratch(p);
+         for (int b = 0; b < PIPE_BLOCKS; b++)
+            if (redo[b]) CKI(run_block(b, attempt == 0));
+         unsigned long long words[PIPE_BLOCKS] = {};
+         CK(cudaMemcpyAsync(words, p.counter + 2, sizeof(words), cudaMemcpyDeviceToHost, st));
+         CK(cudaStreamSynchronize(st));
+         CK(cudaStreamSynchronize(c.copy));
+         // A block whose split rows did not fit has run its whole rows (once) and none of its split rows: only
+         // those blocks are redone, split rows only, so that nothing is accumulated into Z twice; the blocks that
+         // fitted are complete and already with the caller.
+         bool fits = true;
+         long long need_h = 0, need_c = 0;
          nh = nchunks = 0;
+         for (int b = 0; b < PIPE_BLOCKS; b++) {
+            if (bounds[b + 1] <= bounds[b]) { redo[b] = false; continue; }
+            const long long bh = static_cast<long long>(words[b] >> HUB_SHIFT), bc = static_cast<long long>(words[b] & HUB_CHUNK_MASK);
+            redo[b] = redo[b] && (bh > p.hub_cap || bc > p.chunk_cap);
+            fits = fits && !redo[b];
+            need_h = std::max(need_h, bh);
+            need_c = std::max(need_c, bc);
+            nh += bh;
+            nchunks += bc;
+         }
+         if (fits) break;
+         if (attempt == 2) return FUSEDMM_B200_ERR_LIMIT;
+         if (need_h > c.hub_cap) {
+            c.hub_cap = need_h + need_h / 4 + 1024;
+            CKI(ensure_buf(c.hub_row, c.hub_cap * sizeof(long long)));
+            CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
+         }
+         if (need_c > p.chunk_cap) CKI(ensure_buf(c.partials, static_cast<size_t>(need_c + need_c / 8 + 64) * a.k * es));
       }
+      z_returned = true;
+      d2h += a.m * a.k * es;
    }
 
    for (int attempt = 0; attempt < 3 && !z_returned; attempt++) {
       bind_scratch(p);
       if (!async) CK(cudaEventRecord(c.ev0, st));
-      CKI(enqueue_pass(p, attempt == 0 && !rows_done, !async));
+      CKI(enqueue_pass(p, attempt == 0, !async));
       if (async) {
          if (!a.plan) {  // the scratch of a plan call is sized exactly: nothing to report later
             c.async_pending = true;
@@ -943,12 +964,23 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
          if (sop->kind < 0 || sop->kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_UDEF;
          sopk = *sop;
       } else if (hook) {
+         if (g_opt.strict_udef) {
+            fprintf(stderr, "fusedmm_b200: option strict_udef is set: SOP_UDEF needs an explicit scalar function "
+                            "(fusedmm_b200_set_sop or the sop argument), a host SOP_UDEF_FUNC is not examined\n");
+            return FUSEDMM_B200_ERR_UDEF;
+         }
          const bool ok = dtype == 0 ? identify_udef<float>(reinterpret_cast<int (*)(float, float *)>(hook), &sopk)
                                     : identify_udef<double>(reinterpret_cast<int (*)(double, double *)>(hook), &sopk);
          if (!ok) {
             fprintf(stderr, "fusedmm_b200: SOP_UDEF_FUNC is not one of the scalar functions the device implements "
                             "(see FUSEDMM_SOP_* in fusedmm_b200.h)\n");
             return FUSEDMM_B200_ERR_UDEF;
+         }
+         static bool told = false;  // once per process: which device function stands in for the caller's host function
+         if (!told && getenv("FUSEDMM_B200_TRACE")) {
+            told = true;
+            fprintf(stderr, "fusedmm_b200: SOP_UDEF_FUNC matches built-in scalar function %d at the sample points "
+                            "(FUSEDMM_SOP_* in fusedmm_b200.h); the device evaluates that function\n", sopk.kind);
          }
       }
    }
@@ -977,8 +1009,9 @@ static __device__ __align__(256) unsigned char g_static_scratch[FUSEDMM_B200_STA
 
 constexpr int STATIC_MAX_DEVICES = 64;
 constexpr long long STATIC_HUB_CAP = 32768;                    // split rows the hub list has room for
-constexpr size_t STATIC_OFF_TABLE = 256;                       // after the packed counter
-constexpr size_t STATIC_OFF_HUB_ROW = STATIC_OFF_TABLE + SM_TABLE_SIZE * sizeof(double);
+constexpr size_t STATIC_OFF_TABLE_F = 256;                     // after the packed counter: the float sigmoid table,
+constexpr size_t STATIC_OFF_TABLE_D = STATIC_OFF_TABLE_F + SM_TABLE_SIZE * sizeof(float);  // then the double one
+constexpr size_t STATIC_OFF_HUB_ROW = STATIC_OFF_TABLE_D + SM_TABLE_SIZE * sizeof(double);
 constexpr size_t STATIC_OFF_HUB_BASE = STATIC_OFF_HUB_ROW + STATIC_HUB_CAP * sizeof(long long);
 constexpr size_t STATIC_OFF_PARTIALS = STATIC_OFF_HUB_BASE + STATIC_HUB_CAP * sizeof(long long);
 static_assert(STATIC_OFF_PARTIALS % 256 == 0, "the partial sums must start on a 256-byte boundary");
@@ -986,10 +1019,29 @@ static_assert(STATIC_OFF_PARTIALS % 256 == 0, "the partial sums must start on a 
 struct StaticScratchSlot {
    unsigned char *base = nullptr;  // device address of g_static_scratch on this device
    int sm_count = 0;
+   // caps of the latest call that was enqueued on a caller's stream, for fusedmm_b200_stream_status
+   bool async_pending = false;
+   long long async_hub_cap = 0, async_chunk_cap = 0;
 };
 StaticScratchSlot g_static_slot[STATIC_MAX_DEVICES];
 
-// Set-up, once per device, with that device current: ask the runtime where this device keeps the array.
+template <typename T>
+const T *static_host_sigmoid_table()
+{
+   static T table[SM_TABLE_SIZE];
+   static bool ready = false;
+   if (!ready) {
+      for (int i = 0; i < SM_TABLE_SIZE; i++) {
+         T x = static_cast<T>(2.0 * 5.0 * i / SM_TABLE_SIZE - 5.0);
+         table[i] = static_cast<T>(1.0 / (1 + std::exp(-static_cast<double>(x))));
+      }
+      ready = true;
+   }
+   return table;
+}
+
+// Set-up, once per device, with that device current: ask the runtime where this device keeps the array, and put
+// the two sigmoid tables (float and double, each at its own offset) into it.  Later calls copy nothing.
 int static_scratch_base(StaticScratchSlot **out)
 {
    int dev = 0;
@@ -1006,25 +1058,13 @@ int static_scratch_base(StaticScratchSlot **out)
          return FUSEDMM_B200_ERR_CUDA;
       }
       CK(cudaDeviceGetAttribute(&slot.sm_count, cudaDevAttrMultiProcessorCount, dev));
-      slot.base = static_cast<unsigned char *>(ptr);
+      unsigned char *base = static_cast<unsigned char *>(ptr);
+      CK(cudaMemcpy(base + STATIC_OFF_TABLE_F, static_host_sigmoid_table<float>(), SM_TABLE_SIZE * sizeof(float), cudaMemcpyHostToDevice));
+      CK(cudaMemcpy(base + STATIC_OFF_TABLE_D, static_host_sigmoid_table<double>(), SM_TABLE_SIZE * sizeof(double), cudaMemcpyHostToDevice));
+      slot.base = base;
    }
    *out = &slot;
    return 0;
-}
-
-template <typename T>
-const T *static_host_sigmoid_table()
-{
-   static T table[SM_TABLE_SIZE];
-   static bool ready = false;
-   if (!ready) {
-      for (int i = 0; i < SM_TABLE_SIZE; i++) {
-         T x = static_cast<T>(2.0 * 5.0 * i / SM_TABLE_SIZE - 5.0);
-         table[i] = static_cast<T>(1.0 / (1 + std::exp(-static_cast<double>(x))));
-      }
-      ready = true;
-   }
-   return table;
 }
 
 // The row scheduler's four launches on ONE stream (no side stream, no events: creating them allocates),
@@ -1084,11 +1124,8 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
    }
 
    cudaStream_t st = user_stream ? user_stream : cudaStreamLegacy;  // no stream is created
-   if (d.sop == OP_UDEF && sopk.kind == FUSEDMM_SOP_SIGMOID_TABLE_C) {
-      CK(cudaMemcpyAsync(slot->base + STATIC_OFF_TABLE, static_host_sigmoid_table<T>(), SM_TABLE_SIZE * es,
-                         cudaMemcpyHostToDevice, st));
-      p.sop_table = reinterpret_cast<const T *>(slot->base + STATIC_OFF_TABLE);
-   }
+   if (d.sop == OP_UDEF && sopk.kind == FUSEDMM_SOP_SIGMOID_TABLE_C)  // uploaded once per device at set-up
+      p.sop_table = reinterpret_cast<const T *>(slot->base + (sizeof(T) == 4 ? STATIC_OFF_TABLE_F : STATIC_OFF_TABLE_D));
    auto aligned16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
    bool vec_ok = (a.k % W == 0) && (a.ldz % W == 0) && aligned16(p.z) &&
                  (!need_x || ((a.ldx % W == 0) && aligned16(p.x))) && (!need_y || ((a.ldy % W == 0) && aligned16(p.y)));
@@ -1113,10 +1150,13 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
    else launch_any<T>(p, WARPS_PER_CTA, hub_grid, st);
    launch_fixup<T>(p, slot->sm_count, st);
    p.mode = MODE_ROWS;
-   if (vec_ok) launch_vec<T>(d.pattern, G, NV, U, warps, p, row_grid, st);
+   if (vec_ok) { if (!launch_vec<T>(d.pattern, G, NV, U, warps, p, row_grid, st)) return FUSEDMM_B200_ERR_ARG; }
    else launch_any<T>(p, warps, row_grid, st);
    CK(cudaGetLastError());
    long long nh = 0, nchunks = 0;
+   slot->async_pending = user_stream != nullptr;
+   slot->async_hub_cap = p.hub_cap;
+   slot->async_chunk_cap = p.chunk_cap;
    if (!user_stream) {
       unsigned long long packed = 0;
       CK(cudaMemcpyAsync(&packed, p.counter, sizeof(packed), cudaMemcpyDeviceToHost, st));
@@ -1272,6 +1312,24 @@ FMM_DEFINE_G(sgfusedMM_csr_i64, float, int64_t, 0, 64, 64)
 FMM_DEFINE_G(dgfusedMM_csr_i32, double, int32_t, 1, 32, 32)
 FMM_DEFINE_G(dgfusedMM_csr_i64, double, int64_t, 1, 64, 64)
 
+#define FMM_DEFINE_G_UDEF(NAME, VT, IT, DT, PB, IB)                                                   \
+   void NAME(const char tkern, const IT m, const IT n, const IT k, const VT alpha, const IT nnz,      \
+             const IT rows, const IT cols, const VT *val, const IT *indx, const IT *pntrb,            \
+             const IT *pntre, const VT *A, const IT lda, const VT *B, const IT ldb, const VT beta,    \
+             VT *C, const IT ldc, int (*sop_udef)(VT, VT *))                                          \
+   {                                                                                                  \
+      (void)alpha; (void)nnz; (void)rows; (void)cols;                                                 \
+      const int32_t msg = letter_to_message(tkern);                                                   \
+      if (msg < 0) { fprintf(stderr, "Kernel not implemented yet!!!\n"); return; }                    \
+      int st = run_call(DT, PB, IB, msg, m, n, k, nnz, val, indx, pntrb, pntre, A, lda, B, ldb, beta, C,   \
+                        ldc, nullptr, reinterpret_cast<void *>(sop_udef), nullptr);                   \
+      if (st) fprintf(stderr, "fusedmm_b200: %s: %s\n", #NAME, fusedmm_b200_status_string(st));      \
+   }
+FMM_DEFINE_G_UDEF(sgfusedMM_csr_i32_udef, float, int32_t, 0, 32, 32)
+FMM_DEFINE_G_UDEF(sgfusedMM_csr_i64_udef, float, int64_t, 0, 64, 64)
+FMM_DEFINE_G_UDEF(dgfusedMM_csr_i32_udef, double, int32_t, 1, 32, 32)
+FMM_DEFINE_G_UDEF(dgfusedMM_csr_i64_udef, double, int64_t, 1, 64, 64)
+
 int fusedmm_b200_set_sop(int32_t kind, double p0, double p1, double p2)
 {
    if (kind < 0 || kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_ARG;
@@ -1404,6 +1462,19 @@ int fusedmm_b200_plan_destroy(fusedmm_b200_plan *plan)
 int fusedmm_b200_stream_status(void)
 {
    std::lock_guard<std::mutex> lock(g_mu);
+   {  // a call of the entry point that allocates nothing, enqueued on a caller's stream (nothing is allocated here either)
+      int dev = -1;
+      if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < STATIC_MAX_DEVICES && g_static_slot[dev].base &&
+          g_static_slot[dev].async_pending) {
+         StaticScratchSlot &slot = g_static_slot[dev];
+         unsigned long long packed = 0;
+         CK(cudaMemcpy(&packed, slot.base, sizeof(packed), cudaMemcpyDeviceToHost));
+         slot.async_pending = false;
+         if (static_cast<long long>(packed >> HUB_SHIFT) > slot.async_hub_cap ||
+             static_cast<long long>(packed & HUB_CHUNK_MASK) > slot.async_chunk_cap)
+            return FUSEDMM_B200_ERR_LIMIT;  // nnz understated the graph: the split rows of that call were not computed
+      }
+   }
    DeviceCtx *c = nullptr;
    int st = get_ctx(&c);
    if (st) return st;
@@ -1516,6 +1587,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "side_stream")) return &g_opt.side_stream;
    if (!strcmp(name, "force_tiling_rows")) return &g_opt.force_tiling_rows;
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
+   if (!strcmp(name, "strict_udef")) return &g_opt.strict_udef;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
 }
@@ -1524,7 +1596,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    std::lock_guard<std::mutex> lock(g_mu);
    int64_t *s = option_slot(name);
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic || s == &g_opt.side_priority) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic || s == &g_opt.side_priority || s == &g_opt.strict_udef) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.engine && value > 2) return FUSEDMM_B200_ERR_ARG;

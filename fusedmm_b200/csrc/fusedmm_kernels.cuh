@@ -42,7 +42,9 @@ enum : int { SOPK_IDENTITY = 0, SOPK_SIGMOID = 1, SOPK_SIGMOID_TABLE_C = 2, SOPK
 enum : int { MODE_ROWS = 0, MODE_HUB_CHUNKS = 1 };
 
 constexpr unsigned FULL = 0xffffffffu;
-constexpr int HUB_SHIFT = 40;  // packed counter: hub rows in the high 24 bits, chunks in the low 40
+// packed counter: split rows in the high 28 bits, chunks in the low 36.  2^28 split rows need more than 2^36
+// edges at the smallest chunk length, beyond what one GPU's memory holds, so neither field can carry.
+constexpr int HUB_SHIFT = 36;
 constexpr unsigned long long HUB_CHUNK_MASK = (1ull << HUB_SHIFT) - 1ull;
 constexpr int SM_TABLE_SIZE = 2048;
 
@@ -63,7 +65,7 @@ struct Params {
    int mode;                     // MODE_ROWS | MODE_HUB_CHUNKS
    long long chunk;              // rows with more edges than this are split
    // hub-row scratch (written by scan_hub_rows, read by the chunk and fix-up passes)
-   unsigned long long *counter;  // packed (hub rows << 40) | chunks
+   unsigned long long *counter;  // packed (hub rows << HUB_SHIFT) | chunks
    long long *hub_row, *hub_base;
    long long hub_cap, chunk_cap;
    T *partials;                  // chunk_cap x k

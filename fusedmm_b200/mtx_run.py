@@ -8,8 +8,8 @@ so a loop like the one in ``runtime.sh:176-186`` can append the output of this p
 
 The reference builds one executable per kernel; here ``-t`` selects it: ``s`` sigmoid (table look-up, the tester's
 scalar function ``fusedMMtime.cpp:586-633``), ``t`` t-distribution (clamped, ``:640-646``), ``f`` Fruchterman-Reingold
-(``:635-639``), ``m`` SpMM, ``g`` GCN.  "Trusted" is this library's element-strided general kernel
-(option ``force_generic``), "test" its specialised row kernels, both on the GPU with the arrays resident there;
+(``:635-639``), ``m`` SpMM, ``g`` GCN.  "Trusted" is this library's flag-interpreting vector kernel (option
+``force_generic``: the stage codes are read at run time), "test" its kernels specialised for the message, both on the GPU with the arrays resident there;
 times are seconds per call, the median of ``-nrep`` calls measured with CUDA events by the library itself.
 ``-T 1`` also compares the two results, the tester's PASSED/FAILED check (``fusedMMtime.cpp:1690-1712``).
 There is no CPU path: without a CUDA device the program stops with an error.

@@ -110,6 +110,16 @@ extern "C" {
  * FUSEDMM_UNDEFINED_USER_FUNCTION.
  */
 int SOP_UDEF_FUNC(VALUETYPE val, VALUETYPE *out) __attribute__((weak));
+/* The other four hooks, with the reference's signatures (fusedMM.h:135-143 there), so that a program that
+ * defines one with a different signature is diagnosed at compile time as it would be against the
+ * reference's header.  They are never called: a kernel cannot run host code. */
+int VOP_UDEF_FUNC(INDEXTYPE lhs_dim, const VALUETYPE *lhs, INDEXTYPE rhs_dim, const VALUETYPE *rhs,
+                  INDEXTYPE out_dim, VALUETYPE *out);
+int ROP_UDEF_FUNC(INDEXTYPE lhs_dim, const VALUETYPE *lhs, INDEXTYPE rhs_dim, const VALUETYPE *rhs,
+                  VALUETYPE *out);
+int VSC_UDEF_FUNC(INDEXTYPE rhs_dim, const VALUETYPE *rhs, VALUETYPE scal, INDEXTYPE out_dim,
+                  VALUETYPE *out);
+int AOP_UDEF_FUNC(INDEXTYPE rhs_dim, const VALUETYPE *rhs, INDEXTYPE out_dim, VALUETYPE *out);
 
 /* compile-time choice of the typed symbol */
 #define FUSEDMM_B200_IS_DOUBLE   (sizeof(VALUETYPE) == sizeof(double))

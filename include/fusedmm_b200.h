@@ -56,7 +56,8 @@ extern "C" {
  * Which one SOP_UDEF means is chosen, in this order, by
  *   1. an explicit `fusedmm_b200_sop` passed to fusedmm_b200_csr();
  *   2. a host SOP_UDEF_FUNC pointer passed to a *_udef entry point: it is evaluated on the host at a
- *      fixed set of sample points and matched against the built-ins (no match -> status 64);
+ *      fixed set of sample points and matched against the built-ins (no match -> status 64; see option
+ *      "strict_udef" for the limits of that match);
  *   3. the process-wide default set with fusedmm_b200_set_sop() (initially SIGMOID).
  * ---------------------------------------------------------------------------------------------- */
 #define FUSEDMM_SOP_IDENTITY        0  /* out = s                      default body, fusedMMtime.cpp:669-673 */
@@ -159,6 +160,20 @@ FUSEDMM_B200_DECL_G(sgfusedMM_csr_i64, float,  int64_t);
 FUSEDMM_B200_DECL_G(dgfusedMM_csr_i32, double, int32_t);
 FUSEDMM_B200_DECL_G(dgfusedMM_csr_i64, double, int64_t);
 
+/* Same dispatcher with the caller's host SOP_UDEF_FUNC handed over explicitly (the reference's generated
+ * kernels call the hook the program links: kernels/codegen/genkern.base:113,122,487,554); used by the
+ * {s,d}gfusedMM_csr wrappers of include/kernels.h.  `sop_udef` may be NULL (process-wide default). */
+#define FUSEDMM_B200_DECL_G_UDEF(NAME, VT, IT)                                                     \
+   void NAME(const char tkern, const IT m, const IT n, const IT k, const VT alpha, const IT nnz,   \
+             const IT rows, const IT cols, const VT *val, const IT *indx, const IT *pntrb,         \
+             const IT *pntre, const VT *A, const IT lda, const VT *B, const IT ldb, const VT beta, \
+             VT *C, const IT ldc, int (*sop_udef)(VT, VT *))
+
+FUSEDMM_B200_DECL_G_UDEF(sgfusedMM_csr_i32_udef, float,  int32_t);
+FUSEDMM_B200_DECL_G_UDEF(sgfusedMM_csr_i64_udef, float,  int64_t);
+FUSEDMM_B200_DECL_G_UDEF(dgfusedMM_csr_i32_udef, double, int32_t);
+FUSEDMM_B200_DECL_G_UDEF(dgfusedMM_csr_i64_udef, double, int64_t);
+
 /* ------------------------------------------------------------------------------------------------
  * The one function all of the above funnel into.
  *
@@ -223,8 +238,12 @@ int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, in
  *     than about 16.4 million edges at k = 128 floats;
  *   - all launches go to `stream`, or to the legacy default stream when stream is NULL, in which case
  *     the call returns after they have finished;
- *   - the first call on a device looks up the array's address on that device; make that first call
- *     outside any stream capture;
+ *   - the first call on a device looks up the array's address on that device and copies the two 2048-entry
+ *     sigmoid tables (float and double) into it with two small synchronous copies; later calls copy
+ *     nothing.  Make that first call outside any stream capture;
+ *   - with a non-NULL stream the call returns without waiting; if nnz understated the graph, the split rows
+ *     of that call are not computed and fusedmm_b200_stream_status(), called after the stream's work has
+ *     completed, returns FUSEDMM_B200_ERR_LIMIT for it (with a truthful nnz this cannot happen);
  *   - the array is shared by all calls on a device and keeps the previous call's contents (the call
  *     clears the one word that has to start at zero); two calls whose kernels may overlap on the GPU
  *     (different streams without an ordering between them) race on it and must not be issued.
@@ -261,7 +280,12 @@ int fusedmm_b200_plan_csr(const fusedmm_b200_plan *plan, int32_t dtype, int32_t 
 int fusedmm_b200_plan_destroy(fusedmm_b200_plan *plan);
 
 /* After work enqueued with a non-NULL stream has completed: 0, or FUSEDMM_B200_ERR_LIMIT when the
- * hub-row scratch was too small for that call (the scratch has then been enlarged; run the call again). */
+ * hub-row scratch was too small for that call.  The rows with at most hub_chunk edges have then been
+ * computed and the longer rows have not been touched; the scratch has been enlarged.  Running the call
+ * again gives the right Z when the call overwrites Z (beta == 0 on the four optimised messages).  A call
+ * that accumulates (beta != 0, or any other message) has already added its short rows' contributions:
+ * restore Z before running it again.  A positive, truthful nnz sizes the scratch before the launches, so
+ * the case only arises when nnz understates the graph or is 0. */
 int fusedmm_b200_stream_status(void);
 
 /* ------------------------------------------------------------------------------------------------
@@ -330,6 +354,11 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    0: every launch on one stream (12 % slower on the benchmark graph; diagnostic).
  *   "force_tiling_rows"  as force_tiling, for the whole-row launch only (0 = the call's tiling).
  *   "force_generic"  1 = run every message through the flag-interpreting kernel.
+ *   "strict_udef"    0 (default): a host SOP_UDEF_FUNC handed to a *_udef entry point is evaluated at 25 sample
+ *                    points and replaced by the built-in device function that equals it there (none: status 64);
+ *                    a function that differs from the built-in only between or beyond the sample points is not
+ *                    told apart.  1: such a hook is not examined and the call returns status 64; SOP_UDEF then
+ *                    needs fusedmm_b200_set_sop or an explicit sop argument.
  *   "inject_alloc_failure"  n > 0: the n-th device allocation the library attempts from now on fails
  *                    with FUSEDMM_B200_ERR_NOMEM (host-side fault injection for tests; nothing is
  *                    done to the GPU).

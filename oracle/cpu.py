@@ -1,11 +1,14 @@
 """ctypes loaders for the CPU checkers -- TEST INFRASTRUCTURE ONLY.
 
-Three checkers live here, none of which the product (``fusedmm_b200``) may import:
+Four checkers live here, none of which the product (``fusedmm_b200``) may import:
 
 * :class:`Oracle` -- ``oracle/fusedmm_oracle.c``, a C restatement of the general kernel of
   HipGraph/FusedMM (``fusedMM.c:698-739`` and the operator bodies ``fusedMM.c:28-333``).
 * :class:`Reference` -- the reference's own ``fusedMM.c`` compiled by ``oracle/build_ref.sh`` into
   ``oracle/_ref/``; present only where that recipe has run (it needs the reference sources).
+* :class:`ReferenceOpt` -- the reference's optimised OpenMP path (generated SIMD kernels behind
+  ``{s,d}gfusedMM_csr``, ``kernels/src/kernels.c:456-631``) built by ``oracle/build_ref_opt.sh``; it is
+  what the benchmark times as the CPU baseline.
 * :func:`numpy_fusedmm` -- an independent float64 NumPy restatement for hand-sized cases.
 """
 from __future__ import annotations
@@ -50,6 +53,37 @@ def build_reference(reference_dir: str = os.environ.get("FUSEDMM_REFERENCE_DIR",
 
 def reference_available() -> bool:
     return all((REF / f"libfusedmm_ref_{p}_i{b}.so").exists() for p in "sd" for b in (32, 64))
+
+
+def host_simd_level() -> str | None:
+    """SIMD level of this host's CPU the way the reference's ``configure:150-225`` decides it:
+    "avxz" with avx512f and avx512dq, else "avx2", else None (the reference supports nothing less on x86)."""
+    try:
+        flags = set()
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("flags"):
+                flags = set(line.split(":", 1)[1].split())
+                break
+    except OSError:
+        return None
+    if {"avx512f", "avx512dq"} <= flags:
+        return "avxz"
+    if {"avx2", "fma"} <= flags:
+        return "avx2"
+    return None
+
+
+def build_reference_opt(reference_dir: str = os.environ.get("FUSEDMM_REFERENCE_DIR", "/root/reference")) -> bool:
+    """Run ``oracle/build_ref_opt.sh`` when the reference sources are present (a few minutes the first
+    time, nothing when the libraries are up to date); True if the libraries for this host exist."""
+    if Path(reference_dir, "kernels", "codegen", "genkern.base").exists():
+        subprocess.run([str(HERE / "build_ref_opt.sh"), reference_dir], check=True, stdout=subprocess.DEVNULL)
+    return reference_opt_available()
+
+
+def reference_opt_available() -> bool:
+    lvl = host_simd_level()
+    return lvl is not None and all((REF / f"libfusedmm_refopt_{p}_i64_{lvl}.so").exists() for p in "sd")
 
 
 def _ptr(a):
@@ -142,9 +176,53 @@ class Reference:
                   _ptr(pntre), _ptr(x), ldx, _ptr(y), ldy, beta, _ptr(z), ldz)
 
 
-def numpy_sop(s, kind, p=(0.0, 0.0, 0.0)):
-    """float64 scalar functions (same catalogue as ``include/fusedmm_b200.h``), without the table."""
-    s = np.float64(s)
+class ReferenceOpt:
+    """The reference's ``fusedMM_csr`` compiled with ``ENABLE_OPT_FUSEDMM`` and linked with its generated
+    kernels (int64 indices).  The four optimised messages run the generated SIMD kernels when ``ld* == k``
+    and ``k`` is a multiple of the vector length (16/8 floats, 8/4 doubles for AVX-512/AVX2); with
+    ``beta == 0`` they overwrite ``z``.  Everything else falls through to the general kernel."""
+
+    def __init__(self):
+        self.simd = host_simd_level()
+        if not reference_opt_available():
+            raise FileNotFoundError("oracle/_ref holds no optimised reference build for this host "
+                                    "(run oracle/build_ref_opt.sh where the reference sources are available)")
+        self.libs = {p: _C.CDLL(str(REF / f"libfusedmm_refopt_{p}_i64_{self.simd}.so")) for p in "sd"}
+        # the general kernel alone with the same optimising flags (the second timed figure)
+        self.general_libs = {p: _C.CDLL(str(REF / f"libfusedmm_refgen_{p}_i64_{self.simd}.so")) for p in "sd"
+                             if (REF / f"libfusedmm_refgen_{p}_i64_{self.simd}.so").exists()}
+
+    def vlen(self, dtype) -> int:
+        return {("avxz", 4): 16, ("avxz", 8): 8, ("avx2", 4): 8, ("avx2", 8): 4}[(self.simd, np.dtype(dtype).itemsize)]
+
+    def threads(self, n=None):
+        if n is not None:
+            for l in list(self.libs.values()) + list(self.general_libs.values()):
+                l.ref_set_threads(int(n))
+        return self.libs["s"].ref_get_threads()
+
+    def csr(self, imessage, m, n, k, val, indx, pntrb, pntre, x, ldx, y, ldy, beta, z, ldz,
+            sop_kind=1, sop_params=(0.0, 0.0, 0.0), alpha=1.0, nnz=0, general=False):
+        """``general=True`` runs the general kernel alone (always accumulates into ``z``)."""
+        _check_arrays(val, indx, pntrb, pntre, x, y, z)
+        pre, suffix, VT, PT = _types(z.dtype, pntrb.dtype, indx.dtype)
+        if suffix != "i64":
+            raise ValueError("the optimised reference build takes int64 indices only")
+        lib = (self.general_libs if general else self.libs)[pre]
+        lib.ref_set_sop.argtypes = [_C.c_int, _F64, _F64, _F64]
+        lib.ref_set_sop.restype = None
+        lib.ref_set_sop(sop_kind, *sop_params)
+        fn = lib.ref_fusedMM_csr
+        fn.restype = _C.c_int
+        fn.argtypes = ([_I32, PT, PT, PT, VT, PT, PT, PT] + [_C.c_void_p] * 4 +
+                       [_C.c_void_p, PT, _C.c_void_p, PT, VT, _C.c_void_p, PT])
+        return fn(imessage, m, n, k, alpha, nnz, m, n, _ptr(val), _ptr(indx), _ptr(pntrb),
+                  _ptr(pntre), _ptr(x), ldx, _ptr(y), ldy, beta, _ptr(z), ldz)
+
+
+def numpy_sop(s, kind, p=(0.0, 0.0, 0.0), dtype=np.float64):
+    """Scalar functions in ``dtype`` (same catalogue as ``include/fusedmm_b200.h``), without the table."""
+    s = dtype(s)
     with np.errstate(all="ignore"):
         if kind == 0:
             return s
@@ -167,22 +245,23 @@ def numpy_sop(s, kind, p=(0.0, 0.0, 0.0)):
 
 
 def numpy_fusedmm(imessage, m, k, val, indx, pntrb, pntre, x, y, z0, sop_kind=1,
-                  sop_params=(0.0, 0.0, 0.0)):
-    """Independent float64 restatement (vectorised over K, Python loop over edges): small cases only.
-    Follows the stage order of ``fusedMM.c:706-738``; returns a new float64 array."""
+                  sop_params=(0.0, 0.0, 0.0), dtype=np.float64):
+    """Independent restatement in ``dtype`` (float64, or ``np.longdouble`` as the higher-precision evaluation
+    that float64 results are judged against), vectorised over K with a Python loop over edges: small cases only.
+    Follows the stage order of ``fusedMM.c:706-738``; returns a new array of ``dtype``."""
     vop, rop, sop = imessage & 0xF, (imessage >> 4) & 0xF, (imessage >> 8) & 0xF
     vsc, aop = (imessage >> 12) & 0xF, (imessage >> 16) & 0xF
-    X = np.asarray(x, dtype=np.float64)[:, :k]
-    Y = np.asarray(y, dtype=np.float64)[:, :k]
-    Z = np.array(z0, dtype=np.float64)
+    X = np.asarray(x, dtype=dtype)[:, :k]
+    Y = np.asarray(y, dtype=dtype)[:, :k]
+    Z = np.array(z0, dtype=dtype)
     for i in range(m):
         for j in range(int(pntrb[i]), int(pntre[i])):
             xi, yv = X[i], Y[int(indx[j])]
             T = {1: xi, 2: yv, 3: xi + yv, 4: yv - xi, 5: xi - yv, 6: np.maximum(xi, yv),
                  7: np.minimum(xi, yv)}[vop].copy()
-            s = {0: lambda: np.float64(val[j]), 1: lambda: xi @ T, 2: lambda: xi.sum(),
+            s = {0: lambda: dtype(val[j]), 1: lambda: xi @ T, 2: lambda: xi.sum(),
                  3: lambda: T.sum(), 4: lambda: xi @ xi, 5: lambda: T @ T}[rop]()
-            out = numpy_sop(s, sop_kind, sop_params) if sop == 0xF else s
+            out = numpy_sop(s, sop_kind, sop_params, dtype) if sop == 0xF else s
             if vsc == 1:
                 T = out * T
             elif vsc == 2:

@@ -5,7 +5,7 @@
  * (libfusedmm_b200.so) never links, loads or calls it and has no CPU path of its own.
  *
  * Parity status: PINNED.  The reference has no golden vectors, so the pin is the reference itself:
- * oracle/build_ref.sh compiles HipGraph/FusedMM's own fusedMM.c, and tests/test_oracle_vs_ref.py
+ * oracle/build_ref.sh compiles HipGraph/FusedMM's own fusedMM.c, and tests/test_oracle_pin.py
  * requires this restatement to equal it bit for bit on seeded inputs; tests/golden/ holds outputs of
  * that reference build for machines without the reference sources.
  *

@@ -67,3 +67,18 @@ def rel_err(z, zref, k=None):
 
 
 RTOL = {np.dtype(np.float32): 1e-4, np.dtype(np.float64): 1e-10}
+
+
+def within_tolerance(z, want, tol, exact_fn, k=None, slack=4.0):
+    """Acceptance of a GPU result `z` against the oracle's `want` (same precision).  Passes when they agree within
+    `tol` in the metric of rel_err.  Messages that feed a cancelling reduction into a product or a reciprocal
+    (signed inputs, s near 0 or near a pole of the scalar function) amplify the rounding of s in the oracle as much
+    as in the GPU kernel; for those the judge is a higher-precision evaluation of the same inputs, `exact_fn()`
+    (called only when needed): the GPU result must be no further from it than `slack` times the oracle is, or
+    `tol`.  Returns (ok, error vs the oracle, error vs exact or None, the oracle's error vs exact or None)."""
+    e = rel_err(z, want, k)
+    if e <= tol:
+        return True, e, None, None
+    exact = exact_fn()
+    e_gpu, e_or = rel_err(z, exact, k), rel_err(want, exact, k)
+    return e_gpu <= max(tol, slack * e_or), e, e_gpu, e_or

@@ -26,7 +26,7 @@ def declared_symbols():
     text = (ROOT / "include" / "fusedmm_b200.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     names = set(re.findall(r"\b(fusedmm_b200_\w+)\s*\(", text))
-    names |= set(re.findall(r"FUSEDMM_B200_DECL_(?:CSR|CSR_UDEF|G)\((\w+),", text))
+    names |= set(re.findall(r"FUSEDMM_B200_DECL_(?:CSR|CSR_UDEF|G|G_UDEF)\((\w+),", text))
     names |= set(re.findall(r"\bint\s+([sd]fusedMM_csr_\w+)\s*\(", text))
     names.discard("NAME")
     return sorted(names)
@@ -34,7 +34,7 @@ def declared_symbols():
 
 def test_every_declared_symbol_is_exported(lib):
     names = declared_symbols()
-    assert len(names) >= 27 and "fusedMM_csr" in names and "sfusedMM_csr_p64i32" in names
+    assert len(names) >= 31 and "fusedMM_csr" in names and "sfusedMM_csr_p64i32" in names and "dgfusedMM_csr_i32_udef" in names
     for name in names:
         assert hasattr(lib, name), name
 
@@ -66,6 +66,32 @@ def test_headers_compile_as_c_and_cxx_and_agree_with_python(tmp_path):
         assert int(got["MSG"]) == M.MSG_TDIST == 0x11F55
         assert got["GET"] == f"{M.ROP_NORMR} {M.AOP_ADD}"
         assert int(got["ST"]) == M.ERR_VOP
+
+
+def test_kernels_header_compiles_as_c_and_cxx_for_both_index_types(tmp_path):
+    """include/kernels.h maps the reference's {s,d}gfusedMM_csr and trusted_ names (kernels/include/kernels.h:17-43)
+    onto the typed symbols from the caller's INDEXTYPE; with and without VALUETYPE / fusedMM.h in the same program.
+    An unknown kernel letter prints the reference's message and touches no GPU."""
+    libdir = api.LIB_PATH.parent
+    for it in ("int32_t", "int64_t"):
+        for with_fusedmm in (False, True):
+            src = tmp_path / "k.c"
+            src.write_text('#include <stdio.h>\n#include <stdint.h>\n#define INDEXTYPE ' + it + '\n' +
+                           ('#define VALUETYPE float\n#include "fusedMM.h"\n' if with_fusedmm else '') +
+                           '#include "kernels.h"\n' +
+                           ('int SOP_UDEF_FUNC(float v, float *o) { *o = v; return 0; }\n' if with_fusedmm else '') +
+                           'int main(void) {\n'
+                           '  sgfusedMM_csr(\'x\', 0, 0, 0, 0.0f, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0.0f, 0, 0);\n'
+                           '  dgfusedMM_csr(\'x\', 0, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0.0, 0, 0);\n'
+                           '  trusted_sgfusedMM_csr(\'x\', 0, 0, 0, 0.0f, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0.0f, 0, 0);\n'
+                           '  trusted_dgfusedMM_csr(\'g\', 0, 0, 0, 0.0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0.0, 0, 0);\n'
+                           '  puts("done"); return 0; }\n')
+            for cc in ("gcc", "g++"):
+                exe = tmp_path / "k"
+                subprocess.run([cc, "-Wall", "-Werror", "-x", "c" if cc == "gcc" else "c++", str(src), f"-I{ROOT / 'include'}",
+                                f"-L{libdir}", "-lfusedmm_b200", f"-Wl,-rpath,{libdir}", "-o", str(exe)], check=True)
+                run = subprocess.run([str(exe)], check=True, capture_output=True, text=True)
+                assert "done" in run.stdout and run.stderr.count("Kernel not implemented yet!!!") == 3
 
 
 def test_named_messages():

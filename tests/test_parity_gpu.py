@@ -10,7 +10,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from cases import MESSAGES, RTOL, dense, random_csr, rel_err
+from cases import within_tolerance, MESSAGES, RTOL, dense, random_csr, rel_err
 from fusedmm_b200 import api, messages as M, synth
 
 pytestmark = pytest.mark.gpu
@@ -93,7 +93,7 @@ def test_every_message_against_the_oracle(cuda_device, oracle, vt, name, schedul
     rng = np.random.default_rng(sum(map(ord, name + vt.__name__ + scheduler)))
     m, n = 1500, 1100
     generic = msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
-    lo, hi = (0.1, 1.0) if generic else (-0.5, 0.5)  # no cancelling reductions feeding a product
+    lo, hi = -0.5, 0.5  # signed inputs for every message
     for k, it, pt in ((4, np.int32, np.int32), (32, np.int64, np.int64), (64, np.int32, np.int64),
                       (96, np.int32, np.int32), (128, np.int64, np.int64), (200, np.int32, np.int32),
                       (256, np.int32, np.int64), (30, np.int32, np.int32)):
@@ -119,7 +119,18 @@ def test_every_message_against_the_oracle(cuda_device, oracle, vt, name, schedul
         # the table sigmoid is a step function of s (bins of 10/2048): a last-bit difference in s from
         # the order of summation can move an edge to the neighbouring bin, a step of up to 2.5e-3
         tol = 5e-3 if sop == M.SOP_SIGMOID_TABLE_C else RTOL[np.dtype(vt)]
-        assert rel_err(z, want) <= tol, (name, k, it, pt)
+
+        def exact():  # the same inputs one precision up: float64 oracle for float, long double NumPy for double
+            if vt == np.float32:
+                ex = z0.astype(np.float64)
+                oracle.csr(msg, m, n, k, val.astype(np.float64), indx, pntrb, pntre, x.astype(np.float64), k,
+                           y.astype(np.float64), k, 0.0, ex, k, sop_kind=sop, zero_first=not generic)
+                return ex
+            from oracle.cpu import numpy_fusedmm
+            return numpy_fusedmm(msg, m, k, val, indx, pntrb, pntre, x, y, z0, sop_kind=sop, dtype=np.longdouble)
+
+        ok, e, e_gpu, e_or = within_tolerance(z, want, tol, exact)
+        assert ok, (name, k, it, pt, e, e_gpu, e_or)
 
 
 @pytest.mark.parametrize("vt", [np.float32, np.float64])
@@ -641,6 +652,75 @@ def test_unmodified_c_caller_of_the_reference(cuda_device, oracle, tmp_path, vt,
     z = np.fromfile(tmp_path / "z.bin", dtype=nvt).reshape(m, k)
     want = np.zeros((m, k), nvt)
     oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop_kind)
+    assert rel_err(z, want) <= RTOL[np.dtype(nvt)]
+
+
+C_CALLER_LETTER = r"""
+/* A caller of the reference's second public entry (kernels/include/kernels.h:17-43), unchanged: the typed
+   dispatcher by kernel letter, INDEXTYPE from the caller, its own SOP_UDEF_FUNC as the generated kernels expect. */
+#include <stdio.h>
+#include <stdlib.h>
+#include <stdint.h>
+#include <math.h>
+#define VALUETYPE @VT@
+#define INDEXTYPE @IT@
+#include "kernels.h"
+
+int SOP_UDEF_FUNC(VALUETYPE val, VALUETYPE *out) { *out = @SOP@; return 0; }
+
+static void *slurp(const char *name, size_t bytes) {
+   void *p = malloc(bytes ? bytes : 1); FILE *f = fopen(name, "rb");
+   if (!f || fread(p, 1, bytes, f) != bytes) { fprintf(stderr, "cannot read %s\n", name); exit(2); }
+   fclose(f); return p;
+}
+int main(int argc, char **argv) {
+   INDEXTYPE m = atol(argv[1]), n = atol(argv[2]), k = atol(argv[3]), nnz = atol(argv[4]);
+   INDEXTYPE *rowptr = slurp("rowptr.bin", (m + 1) * sizeof(INDEXTYPE)), *indx = slurp("indx.bin", nnz * sizeof(INDEXTYPE));
+   VALUETYPE *val = slurp("val.bin", nnz * sizeof(VALUETYPE)), *x = slurp("x.bin", m * k * sizeof(VALUETYPE));
+   VALUETYPE *y = slurp("y.bin", n * k * sizeof(VALUETYPE)), *z = calloc(m * k, sizeof(VALUETYPE));
+   @PRE@gfusedMM_csr('@LETTER@', m, n, k, 1.0, nnz, m, n, val, indx, rowptr, rowptr + 1, x, k, y, k, 0.0, z, k);
+   trusted_@PRE@gfusedMM_csr('g', m, n, k, 1.0, nnz, m, n, val, indx, rowptr, rowptr + 1, x, k, y, k, 1.0, z, k);
+   FILE *o = fopen("z.bin", "wb"); fwrite(z, sizeof(VALUETYPE), m * k, o); fclose(o);
+   return 0;
+}
+"""
+
+
+@pytest.mark.parametrize("vt,it,letter,sop_c,sop_kind", [
+    ("float", "int32_t", "t", "1.0 / (1.0 + val)", M.SOP_TDIST),
+    ("double", "int64_t", "s", "1.0 / (1.0 + exp(-val))", M.SOP_SIGMOID),
+    ("float", "int64_t", "m", "val", M.SOP_IDENTITY)])
+def test_unmodified_c_caller_of_the_letter_dispatcher(cuda_device, oracle, tmp_path, vt, it, letter, sop_c, sop_kind):
+    """A C program written against the reference's kernels.h ({s,d}gfusedMM_csr and the trusted_ names, INDEXTYPE
+    from the caller, its own SOP_UDEF_FUNC) is compiled against include/kernels.h, linked and run: the lettered
+    message with beta = 0 followed by the GCN message with beta = 1 on the same Z."""
+    import subprocess
+    root = Path(__file__).resolve().parents[1]
+    nvt = np.float32 if vt == "float" else np.float64
+    nit = np.int64 if it == "int64_t" else np.int32
+    rng = np.random.default_rng(78)
+    m, n, k = 500, 400, 64
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 9, nit, nit, hub=1200)
+    rowptr = as_rowptr(pntrb, pntre)
+    nnz = int(rowptr[-1])
+    indx, val = indx[:nnz].copy(), val[:nnz].astype(nvt)
+    x, y = np.nan_to_num(dense(rng, m, k, k, nvt)), np.nan_to_num(dense(rng, n, k, k, nvt))
+    for name, a in (("rowptr", rowptr), ("indx", indx), ("val", val), ("x", x), ("y", y)):
+        a.tofile(tmp_path / f"{name}.bin")
+    src = C_CALLER_LETTER
+    for key, rep in (("@VT@", vt), ("@IT@", it), ("@SOP@", sop_c), ("@LETTER@", letter), ("@PRE@", "s" if vt == "float" else "d")):
+        src = src.replace(key, rep)
+    (tmp_path / "caller.c").write_text(src)
+    libdir = api.LIB_PATH.parent
+    subprocess.run(["gcc", "-O1", "-Wall", "-Werror", "caller.c", f"-I{root / 'include'}", f"-L{libdir}", "-lfusedmm_b200",
+                    f"-Wl,-rpath,{libdir}", "-lm", "-o", "caller"], cwd=tmp_path, check=True)
+    run = subprocess.run(["./caller", str(m), str(n), str(k), str(nnz)], cwd=tmp_path, capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    z = np.fromfile(tmp_path / "z.bin", dtype=nvt).reshape(m, k)
+    msg = {"t": M.MSG_TDIST, "s": M.MSG_SIGMOID, "m": M.MSG_SPMM}[letter]
+    want = np.zeros((m, k), nvt)
+    oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop_kind)
+    oracle.csr(M.MSG_GCN, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 1.0, want, k, sop_kind=0, zero_first=False)
     assert rel_err(z, want) <= RTOL[np.dtype(nvt)]
 
 
