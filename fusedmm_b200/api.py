@@ -186,6 +186,20 @@ def gfusedMM_csr(tkern, m, n, k, alpha, nnz, rows, cols, val, indx, pntrb, pntre
        ptrs[1], ptrs[2], ptrs[3], ptrs[4], lda, ptrs[5], ldb, beta, ptrs[6], ldc)
 
 
+def zero_empty_rows(pntrb, pntre, z, k, ldz, stream=None):
+    """``fusedmm_b200_zero_empty_rows``: Z_u = 0 for the rows without edges among the ``len(pntrb)`` rows that
+    ``pntrb``/``pntre``/``z`` start at (device tensors); returns the status code."""
+    L = lib()
+    ptrs, dts = zip(*[_describe(a) for a in (pntrb, pntre, z)])
+    if dts[0] != dts[1]:
+        raise TypeError("pntrb and pntre must share one integer type")
+    fn = L.fusedmm_b200_zero_empty_rows
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    return fn(0 if np.dtype(dts[2]) == np.float32 else 1, np.dtype(dts[0]).itemsize * 8, len(pntrb), k, ptrs[0], ptrs[1],
+              ptrs[2], ldz, stream)
+
+
 def shard_rows(pntrb, pntre, nshards, row_weight=0):
     """Contiguous row ranges of equal cost, a row costing its edges plus ``row_weight``
     (``fusedmm_b200_shard_rows_weighted_*``; 0 = balanced by edges alone); host NumPy row pointers."""

@@ -186,7 +186,7 @@ struct DeviceCtx {
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0;
+           strict_udef = 0, multi_skip_empty_rows = 1;
 };
 
 std::mutex g_mu;
@@ -625,6 +625,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          p.z_peer[i] = static_cast<T *>(a.z_peers[i]);
       }
    }
+   p.skip_empty_remote = (p.z_mc || p.n_peers > 0) && g_opt.multi_skip_empty_rows;
    if (d.sop == OP_UDEF && sopk.kind == FUSEDMM_SOP_SIGMOID_TABLE_C) {
       DevBuf &tb = sizeof(T) == 4 ? c.table_f : c.table_d;
       if (!tb.ptr) {
@@ -1330,6 +1331,22 @@ FMM_DEFINE_G_UDEF(sgfusedMM_csr_i64_udef, float, int64_t, 0, 64, 64)
 FMM_DEFINE_G_UDEF(dgfusedMM_csr_i32_udef, double, int32_t, 1, 32, 32)
 FMM_DEFINE_G_UDEF(dgfusedMM_csr_i64_udef, double, int64_t, 1, 64, 64)
 
+int fusedmm_b200_zero_empty_rows(int32_t dtype, int32_t ptr_bits, int64_t m, int64_t k, const void *pntrb,
+                                 const void *pntre, void *z, int64_t ldz, void *stream)
+{
+   if ((dtype != 0 && dtype != 1) || (ptr_bits != 32 && ptr_bits != 64) || m < 0 || k < 0 || ldz < k) return FUSEDMM_B200_ERR_ARG;
+   if (m == 0 || k == 0) return 0;
+   if (!pntrb || !pntre || !z) return FUSEDMM_B200_ERR_ARG;
+   if (!is_device_pointer(pntrb) || !is_device_pointer(pntre) || !is_device_pointer(z)) return FUSEDMM_B200_ERR_ARG;
+   cudaStream_t st = static_cast<cudaStream_t>(stream);
+   const unsigned int grid = static_cast<unsigned int>((m + 255) / 256);
+   if (dtype == 0) zero_empty_rows_kernel<float><<<grid, 256, 0, st>>>(pntrb, pntre, ptr_bits == 64, m, k, static_cast<float *>(z), ldz);
+   else zero_empty_rows_kernel<double><<<grid, 256, 0, st>>>(pntrb, pntre, ptr_bits == 64, m, k, static_cast<double *>(z), ldz);
+   CK(cudaGetLastError());
+   if (!stream) CK(cudaStreamSynchronize(st));
+   return 0;
+}
+
 int fusedmm_b200_set_sop(int32_t kind, double p0, double p1, double p2)
 {
    if (kind < 0 || kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_ARG;
@@ -1588,6 +1605,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "force_tiling_rows")) return &g_opt.force_tiling_rows;
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "strict_udef")) return &g_opt.strict_udef;
+   if (!strcmp(name, "multi_skip_empty_rows")) return &g_opt.multi_skip_empty_rows;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
 }
@@ -1596,7 +1614,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    std::lock_guard<std::mutex> lock(g_mu);
    int64_t *s = option_slot(name);
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic || s == &g_opt.side_priority || s == &g_opt.strict_udef) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.engine && value > 2) return FUSEDMM_B200_ERR_ARG;

@@ -83,6 +83,9 @@ struct Params {
    // GPU of the group, this GPU included): a finished row is then stored ONCE with multimem.st and the
    // switch delivers it to every GPU, so a rank sends its shard once instead of once per peer
    T *z_mc;
+   // 1: rows without edges are not sent to the other GPUs (every GPU holds the row pointers and zeroes, or
+   // keeps, those rows of its own copy itself: zero_empty_rows_kernel); their result is stored locally only
+   int skip_empty_remote;
 };
 
 // ---------------------------------------------------------------------------------------------------
@@ -560,11 +563,13 @@ fused_vec_kernel(const Params<T> p)
 #pragma unroll
                   for (int i = 0; i < W; i++) acc[v][i] = aop_apply(aop, old[i], acc[v][i]);
                }
-               if (p.z_mc) {
+               const bool remote = !(p.skip_empty_remote && w.eb == w.ee);
+               if (p.z_mc && remote) {
                   st_vec_multicast(p.z_mc + w.row * p.ldz + e0, acc[v]);
                } else {
                   st_vec(dst + e0, acc[v]);
-                  for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
+                  if (remote)
+                     for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
                }
             }
          }
@@ -589,6 +594,7 @@ fused_vec_kernel(const Params<T> p)
 
       if (lane < G) {  // slot 0 holds (like every slot) the finished sums
          const bool to_z = w.dst_item < 0;
+         const bool remote = !(p.skip_empty_remote && w.eb == w.ee);
          T *dst = to_z ? p.z + w.row * p.ldz : p.partials + w.dst_item * p.k;
 #pragma unroll
          for (int v = 0; v < NV; v++) {
@@ -600,11 +606,11 @@ fused_vec_kernel(const Params<T> p)
 #pragma unroll
                   for (int i = 0; i < W; i++) acc[v][i] = aop_apply(aop, old[i], acc[v][i]);
                }
-               if (to_z && p.z_mc) {
+               if (to_z && p.z_mc && remote) {
                   st_vec_multicast(p.z_mc + w.row * p.ldz + e0, acc[v]);
                } else {
                   st_vec(dst + e0, acc[v]);
-                  if (to_z)
+                  if (to_z && remote)
                      for (int q = 0; q < p.n_peers; q++) st_vec(p.z_peer[q] + w.row * p.ldz + e0, acc[v]);
                }
             }
@@ -655,6 +661,7 @@ fused_any_kernel(const Params<T> p)
       }
       const T *xr = p.x + w.row * p.ldx;  // dereferenced only when a stage reads X
       const bool to_z = w.dst_item < 0;
+      const bool remote = !(p.skip_empty_remote && w.eb == w.ee);
       T *dst = to_z ? p.z + w.row * p.ldz : p.partials + w.dst_item * p.k;
       const bool need_x = vop_reads_x(vop) || rop_reads_x(rop);
 
@@ -698,11 +705,11 @@ fused_any_kernel(const Params<T> p)
             if (t < p.k) {
                T r = acc[e];
                if (to_z && p.accumulate) r = aop_apply(aop, dst[t], r);
-               if (to_z && p.z_mc) {
+               if (to_z && p.z_mc && remote) {
                   st_multicast(p.z_mc + w.row * p.ldz + t, r);
                } else {
                   dst[t] = r;
-                  if (to_z)
+                  if (to_z && remote)
                      for (int q = 0; q < p.n_peers; q++) p.z_peer[q][w.row * p.ldz + t] = r;
                }
             }
@@ -750,6 +757,32 @@ hub_fixup_kernel(const Params<T> p)
             zr[t] = a;
             for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = a;
          }
+      }
+   }
+}
+
+// Z_row = 0 for every row without edges: what a call with beta == 0 leaves in such rows.  A GPU of a multi-GPU
+// run does this to the rows of the OTHER GPUs' shards in its own copy of Z, so that those rows need not cross
+// NVLink.  One warp per 32 rows: each lane looks at one row, then the warp zeroes the empty ones together.
+template <typename T>
+__global__ void __launch_bounds__(256)
+zero_empty_rows_kernel(const void *pntrb, const void *pntre, int ptr64, long long m, long long k, T *z, long long ldz)
+{
+   const int lane = threadIdx.x & 31;
+   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+   const long long r = warp * 32 + lane;
+   const bool empty = r < m && ld_index(pntre, r, ptr64) <= ld_index(pntrb, r, ptr64);
+   unsigned mask = __ballot_sync(FULL, empty);
+   const bool vec = (k % VecOf<T>::W == 0) && (ldz % VecOf<T>::W == 0) && ((reinterpret_cast<uintptr_t>(z) & 15) == 0);
+   while (mask) {
+      const int src = __ffs(mask) - 1;
+      mask &= mask - 1;
+      T *zr = z + (warp * 32 + src) * ldz;
+      if (vec) {
+         const T zero[VecOf<T>::W] = {};
+         for (long long t = static_cast<long long>(lane) * VecOf<T>::W; t < k; t += 32 * VecOf<T>::W) st_vec(zr + t, zero);
+      } else {
+         for (long long t = lane; t < k; t += 32) zr[t] = T(0);
       }
    }
 }

@@ -208,6 +208,13 @@ int fusedmm_b200_csr(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t 
  * an NVSwitch multicast mapping of Z (it covers this GPU's copy too); each finished row is then stored
  * once with multimem.st and the switch delivers it to every GPU, so a rank sends its rows once, not
  * once per peer.  No counterpart in the reference (which is single-process, fusedMM.c:487-744).
+ *
+ * Rows without edges are NOT sent (option "multi_skip_empty_rows", default 1): their result is a constant
+ * that every GPU can produce itself from the row pointers it already holds, and on R-MAT graphs they are a
+ * quarter to half of all rows.  The call stores such a row (zeros when beta == 0, the unchanged Z_u otherwise)
+ * into this GPU's `z` only.  The other GPUs bring their own copies up to date with
+ * fusedmm_b200_zero_empty_rows over the rows of the foreign shards when beta == 0; with beta != 0 there is
+ * nothing to do as long as every GPU's Z held the same values on entry.
  * ---------------------------------------------------------------------------------------------- */
 int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage,
                            int64_t m, int64_t n, int64_t k, double alpha, int64_t nnz, int64_t rows,
@@ -215,6 +222,13 @@ int fusedmm_b200_csr_multi(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, in
                            const void *pntre, const void *x, int64_t ldx, const void *y, int64_t ldy,
                            double beta, void *z, int64_t ldz, const fusedmm_b200_sop *sop, void *stream,
                            int32_t n_peers, void *const *z_peers, void *z_multicast);
+
+/* Z_u = 0 for every row u < m with pntre[u] <= pntrb[u], on `stream` (NULL: the default stream, and the call
+ * waits): what fusedMM_csr with beta == 0 leaves in rows without edges (kernels/codegen/genkern.base:287-295).
+ * Device arrays only.  Used by the GPUs of a multi-GPU run on the rows of the other GPUs' shards (see
+ * fusedmm_b200_csr_multi).  No counterpart in the reference. */
+int fusedmm_b200_zero_empty_rows(int32_t dtype, int32_t ptr_bits, int64_t m, int64_t k, const void *pntrb,
+                                 const void *pntre, void *z, int64_t ldz, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * fusedmm_b200_csr for callers that must not allocate.
@@ -354,6 +368,8 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    0: every launch on one stream (12 % slower on the benchmark graph; diagnostic).
  *   "force_tiling_rows"  as force_tiling, for the whole-row launch only (0 = the call's tiling).
  *   "force_generic"  1 = run every message through the flag-interpreting kernel.
+ *   "multi_skip_empty_rows"  1 (default): fusedmm_b200_csr_multi does not send rows without edges to the other
+ *                    GPUs (see there); 0: every row of the shard is sent.
  *   "strict_udef"    0 (default): a host SOP_UDEF_FUNC handed to a *_udef entry point is evaluated at 25 sample
  *                    points and replaced by the built-in device function that equals it there (none: status 64);
  *                    a function that differs from the built-in only between or beyond the sample points is not

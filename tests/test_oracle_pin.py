@@ -117,3 +117,45 @@ def test_zero_first_matches_optimised_kernel_semantics(oracle):
     oracle.csr(M.MSG_GCN, m, n, k, val.astype(np.float32), indx, pntrb, pntre, x, k, x, k, 0.0, z2, k,
                zero_first=False)
     assert np.array_equal(z, z2)
+
+
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_optimised_reference_build_agrees_with_the_oracle(oracle, vt):
+    """The timed CPU baseline (the reference's generated OpenMP kernels, oracle/build_ref_opt.sh) computes what the
+    oracle computes: the four optimised messages within the tolerance the GPU is held to (the vector kernels sum in
+    another order than the general kernel), beta = 0 overwriting Z and beta = 1 accumulating, and a message without
+    an optimised kernel falling through to the general kernel bit for bit."""
+    from oracle.cpu import ReferenceOpt, reference_opt_available
+    if not reference_opt_available():
+        pytest.skip("oracle/_ref holds no optimised reference build (needs the reference sources; run oracle/build_ref_opt.sh)")
+    opt = ReferenceOpt()
+    opt.threads(3)
+    rng = np.random.default_rng(5)
+    m, n = 700, 600
+    pntrb, pntre, indx, val = random_csr(rng, m, n, 8, np.int64, np.int64, hub=900)
+    val = val.astype(vt)
+    for k in (opt.vlen(vt), 64, 128, 512 + 2 * opt.vlen(vt)):   # one vector, unrolled kernels, beyond bestK (rolled tail)
+        x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+        for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_TDIST, M.SOP_FR), (M.MSG_TDIST, M.SOP_TDIST),
+                         (M.MSG_SPMM, 0), (M.MSG_GCN, 0)):
+            for beta in (0.0, 1.0):
+                if beta == 0.0 and k > 512:
+                    continue  # the reference's rolled tail accumulates onto stale Z when beta == 0 (genkern.base:392-393)
+                z0 = rng.uniform(-1, 1, size=(m, k)).astype(vt)
+                want, got = z0.copy(), z0.copy()
+                assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, beta, want, k, sop_kind=sop,
+                                  zero_first=(beta == 0.0)) == 0
+                assert opt.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, beta, got, k, sop_kind=sop) == 0
+                assert rel_err(got, want) <= RTOL[np.dtype(vt)], (hex(msg), k, beta)
+    k = 32
+    x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+    msg = MESSAGES["add_addrhs_vscadd_add"]
+    z0 = rng.uniform(-1, 1, size=(m, k)).astype(vt)
+    got = z0.copy()
+    assert opt.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, got, k) == 0
+    gen = z0.copy()
+    assert opt.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, gen, k, general=True) == 0
+    assert np.array_equal(got, gen)
+    want = z0.copy()
+    assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, zero_first=False) == 0
+    assert rel_err(got, want) <= RTOL[np.dtype(vt)]

@@ -513,6 +513,55 @@ def test_properties_at_full_size_of_config_3(cuda_device):
     assert torch.equal(z1, z2) and bool(torch.isfinite(z1).all())
 
 
+@pytest.mark.parametrize("vt", ["f32", "f64"])
+def test_properties_at_full_size_of_config_5(cuda_device, vt):
+    """R-MAT scale 24 (16 777 216 vertices, about 520 million edges: int64 row pointers, int32 column ids, edge
+    positions beyond 2^29 and n*ldy = 2^31), K = 128, float and double: neighbour counts are exact, the sigmoid
+    message is finite, reproducible bit for bit and independent of how the rows are sharded, and a seeded sample of
+    rows equals a float64 evaluation with torch on the device within the tolerance."""
+    import torch
+    free, _ = torch.cuda.mem_get_info()
+    if free < (90 << 30):
+        pytest.skip("needs about 90 GB of free device memory")
+    dtype = torch.float32 if vt == "f32" else torch.float64
+    cfg, csr, x = synth.make_config("c5_sigmoid_rmat24_k128", device=cuda_device, dtype=dtype)
+    n, k = csr.n, cfg["k"]
+    assert n == 1 << 24 and csr.nnz > (1 << 28) and csr.rowptr.dtype == torch.int64 and csr.indx.dtype == torch.int32
+    pb, pe = csr.pntrb.contiguous(), csr.pntre.contiguous()
+    deg = csr.degrees()
+    z = torch.empty((n, k), dtype=dtype, device=cuda_device)
+    ones = torch.ones((n, k), dtype=dtype, device=cuda_device)
+    assert api.fusedMM_csr(M.MSG_GCN, n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, x, k, ones, k, 0.0, z, k) == 0
+    assert api.call_info().hub_rows > 0
+    for col in (0, k // 2, k - 1):
+        assert torch.equal(z[:, col], deg.to(dtype))
+    del ones
+    z1 = torch.empty((n, k), dtype=dtype, device=cuda_device)
+    assert api.fusedMM_csr(cfg["msg"], n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, x, k, x, k, 0.0, z1, k,
+                           sop=cfg["sop"]) == 0
+    assert api.fusedMM_csr(cfg["msg"], n, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb, pe, x, k, x, k, 0.0, z, k,
+                           sop=cfg["sop"]) == 0
+    assert torch.equal(z, z1) and bool(torch.isfinite(z1).all())
+    z.fill_(-1.0)
+    bounds = api.shard_rows(pb.cpu().numpy(), pe.cpu().numpy(), 8)
+    for g in range(8):
+        r0, r1 = int(bounds[g]), int(bounds[g + 1])
+        assert api.fusedMM_csr(cfg["msg"], r1 - r0, n, k, 1.0, csr.nnz, n, n, csr.val, csr.indx, pb[r0:], pe[r0:],
+                               x[r0:], k, x, k, 0.0, z[r0:], k, sop=cfg["sop"]) == 0
+    assert torch.equal(z, z1)
+    # a sample of rows (the longest row, the last row with edges, 64 seeded ones) in float64 with torch
+    rows = torch.cat([deg.argmax().reshape(1), (deg > 0).nonzero().flatten()[-1:],
+                      torch.randint(0, n, (64,), generator=torch.Generator().manual_seed(5)).to(cuda_device)])
+    worst = 0.0
+    for r in rows.tolist():
+        cols = csr.indx[int(csr.rowptr[r]):int(csr.rowptr[r + 1])].to(torch.int64)
+        xr, yr = x[r].double(), x[cols].double()
+        want = (torch.sigmoid(yr @ xr)[:, None] * yr).sum(dim=0)
+        scale = torch.maximum(want.abs(), want.abs().max()).clamp_min(1e-30)
+        worst = max(worst, float(((z1[r].double() - want).abs() / scale).max()))
+    assert worst <= (1e-4 if vt == "f32" else 1e-10), worst
+
+
 def test_32_bit_indices_with_more_than_2_31_elements_of_y(cuda_device):
     """Configuration 4 at full size (4 194 304 vertices, K = 512) with every index array int32: n*ldy = 2^31,
     so `cid*ldy` must be computed in 64 bits (an int32 build of the reference overflows here).  SpMM with the
