@@ -17,6 +17,7 @@ float32, int64 row pointers with int32 column ids.  Prints ONE JSON line (rank 0
              host cores, on a row sample of the same graph, and the reference's general kernel as a second figure
   configs    (N = 1, default workload only) one compact record per other benchmark configuration, measured in the
              same run: ms, GFLOP/s, edges/s, roofline fraction, clocks, CPU figure, error against the reference
+  generic    (same condition) messages outside the four optimised patterns on the FR configuration's graph
 With N > 1 (under torchrun) the rows are cut into N cost-balanced shards, one per rank, Y is replicated and the Z
 shards are exchanged over NVLink inside the timed region ("scaling": "strong").
 `--impl reference` times only the reference's CPU implementation, same metric, unit and config.
@@ -474,17 +475,23 @@ def bench_gpu(args, ctx, cfgname, dtype, scale, steps, warmup, with_e2e, cpu_tar
     kms = {"scan": [], "rows": [], "chunks": [], "fixup": [], "main": []}
     launches_per_step = 0
     zk = z if pz is None else torch.empty((r1 - r0, k), dtype=tdtype, device=dev)  # not into the shared Z: peers read it
-    for _ in range(5):
-        if flush is not None:
-            flush.fill_(2)
-            torch.cuda.synchronize()
-        st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all[r0:], pe_all[r0:], x[r0:],
-                             k, x, k, 0.0, zk[r0:] if pz is None else zk, k, sop=sop if sop is not None else 0)
-        assert st == 0
-        info = api.call_info()
-        launches_per_step = info.kernel_launches
-        for nm in kms:
-            kms[nm].append(getattr(info, "ms_" + nm))
+    # first with an event after every launch (the breakdown), then with the outer events only: the events between
+    # the kernels keep the library from pairing their launches, so only the second set is the real span
+    for detail in (1, 0):
+        api.set_option("timing_detail", detail)
+        for _ in range(5):
+            if flush is not None:
+                flush.fill_(2)
+                torch.cuda.synchronize()
+            st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb_all[r0:], pe_all[r0:], x[r0:],
+                                 k, x, k, 0.0, zk[r0:] if pz is None else zk, k, sop=sop if sop is not None else 0)
+            assert st == 0
+            info = api.call_info()
+            launches_per_step = info.kernel_launches
+            for nm in kms:
+                if (nm == "main") != bool(detail):
+                    kms[nm].append(getattr(info, "ms_" + nm))
+    api.set_option("timing_detail", 1)
     kmed = {nm: float(np.median(v)) for nm, v in kms.items()}
     peak, peak_kind = load_peaks()
     alg_bytes = synth.algorithmic_bytes(msg, my_edges, r1 - r0, k, es, 4, 8)
@@ -551,6 +558,71 @@ def bench_gpu(args, ctx, cfgname, dtype, scale, steps, warmup, with_e2e, cpu_tar
     return out
 
 
+def bench_generic(ctx, steps=10):
+    """Messages outside the four optimised patterns, on the FR configuration's graph (R-MAT scale 20, K = 256): each
+    through the kernel built for it at run time (option jit = 2) and through the flag-interpreting kernel (jit = 0),
+    and the FR message itself forced down both routes, to be compared with its built-in kernel."""
+    torch, api, synth, M, dev = ctx["torch"], ctx["api"], ctx["synth"], ctx["M"], ctx["dev"]
+    cfg, csr, x = synth.make_config("c2_fr_rmat20_k256", device=dev)
+    n, k, nnz = cfg["n"], cfg["k"], csr.nnz
+    pb, pe = csr.pntrb.contiguous(), csr.pntre.contiguous()
+    peak, _ = load_peaks()
+    stream = torch.cuda.Stream()
+    cases = [("fr_message_as_a_generic_one", M.MSG_TDIST, M.SOP_FR, 2),
+             ("add_normr_tdist_mul_max", M.VOP_ADD | M.ROP_NORMR | M.SOP_UDEF | M.VSC_MUL | M.AOP_MAX, M.SOP_TDIST, 0),
+             ("min_addrhs_copy_vscadd_min", M.VOP_MIN | M.ROP_ADD_RHS | M.SOP_COPY | M.VSC_ADD | M.AOP_MIN, 0, 0),
+             ("subl_dot_sigmoid_mul_add", M.VOP_SUBL | M.ROP_DOT | M.SOP_UDEF | M.VSC_MUL | M.AOP_ADD, M.SOP_SIGMOID, 0)]
+    out = []
+
+    def timed(msg, sop, z):
+        def call():
+            st = api.fusedMM_csr(msg, n, n, k, 1.0, nnz, n, n, csr.val, csr.indx, pb, pe, x, k, x, k, 0.0, z, k, sop=sop,
+                                 stream=stream.cuda_stream)
+            assert st == 0, api.status_string(st)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                call()
+            jit = api.call_info().jit_kernel
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            z.zero_()
+            e0.record()
+            for _ in range(steps):
+                call()
+            e1.record()
+            stream.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            z.zero_()
+            call()
+            stream.synchronize()
+        return ms, jit
+
+    try:
+        for name, msg, sop, force in cases:
+            bytes_ = synth.algorithmic_bytes(msg, nnz, n, k, 4, 4, 8)
+            za = torch.zeros((n, k), device=dev)
+            zb = torch.zeros((n, k), device=dev)
+            api.set_option("force_generic", force)
+            api.set_option("jit", 2)
+            ms_jit, used = timed(msg, sop, za)
+            api.set_option("jit", 0)
+            api.set_option("force_generic", 1 if force else 0)
+            ms_rt, _ = timed(msg, sop, zb)
+            scale = torch.maximum(zb.abs(), zb.abs().amax(dim=1, keepdim=True)).clamp_min(1e-30)
+            err = float(((za - zb).abs() / scale).max())
+            out.append({"message": name, "imessage": hex(msg), "sop": sop, "ms": ms_jit, "run_time_built_kernel": bool(used),
+                        "generic_frac": bytes_ / (ms_jit * 1e-3) * 1e-9 / peak,
+                        "flag_interpreting_ms": ms_rt, "flag_interpreting_frac": bytes_ / (ms_rt * 1e-3) * 1e-9 / peak,
+                        "max_rel_diff_between_the_two": err, "finite": bool(torch.isfinite(za).all())})
+            del za, zb
+    finally:
+        api.set_option("force_generic", 0)
+        api.set_option("jit", 1)
+    api.lib().fusedmm_b200_release()
+    torch.cuda.empty_cache()
+    return {"graph": "c2_fr_rmat20_k256 (R-MAT scale 20, K = 256, float32)", "steps": steps, "jit": api.jit_stats(), "messages": out}
+
+
 def compact(rec):
     """One side configuration as a short record."""
     cb = rec["cpu_baseline"] or {}
@@ -578,6 +650,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-array (end-to-end) leg; e2e is then null")
     ap.add_argument("--no-configs", action="store_true", help="skip the records of the other configurations")
+    ap.add_argument("--generic-only", action="store_true", help="only the section on messages outside the four patterns")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     default_run = args.workload is None and args.scale is None and args.dtype == "f32"
@@ -648,6 +721,9 @@ def main():
 
     ctx = {"torch": torch, "api": api, "synth": synth, "M": M, "fdist": fdist, "dist": dist, "rank": rank, "world": world,
            "dev": dev, "cpu": cpu}
+    if args.generic_only:
+        print(json.dumps(bench_generic(ctx)))
+        return
     big = synth.CONFIGS[cfgname]["graph"][1] >= 22 and not args.scale
     steps = args.steps
     out = bench_gpu(args, ctx, cfgname, args.dtype, args.scale, steps, args.warmup, with_e2e=not args.no_e2e,
@@ -671,6 +747,7 @@ def main():
                             cpu_target_s=1.5, cpu_steps=2)
             recs.append(compact(rec))
         out["configs"] = recs
+        out["generic"] = bench_generic(ctx)
 
     if rank == 0:
         sys.stdout.flush()

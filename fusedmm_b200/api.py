@@ -33,7 +33,8 @@ class CallInfo(C.Structure):
                 ("vectors_per_lane", C.c_int32), ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64),
                 ("hub_rows", C.c_int64), ("hub_chunks", C.c_int64), ("device_ms", C.c_float),
                 ("sop_kind", C.c_int32), ("ms_scan", C.c_float), ("ms_rows", C.c_float),
-                ("ms_chunks", C.c_float), ("ms_fixup", C.c_float), ("engine", C.c_int32), ("ms_main", C.c_float)]
+                ("ms_chunks", C.c_float), ("ms_fixup", C.c_float), ("engine", C.c_int32), ("ms_main", C.c_float),
+                ("jit_kernel", C.c_int32)]
 
 
 def lib() -> C.CDLL:
@@ -76,6 +77,19 @@ def get_option(name: str) -> int:
     if st:
         raise FusedMMError(f"unknown option {name!r}")
     return v.value
+
+
+def jit_prepare(imessage: int, k: int, dtype=np.float32) -> int:
+    """``fusedmm_b200_jit_prepare``: build the kernel specialised for a message ahead of its first call."""
+    fn = lib().fusedmm_b200_jit_prepare
+    fn.argtypes = [C.c_int32, C.c_int32, C.c_int64]
+    return fn(0 if np.dtype(dtype) == np.float32 else 1, int(imessage), int(k))
+
+
+def jit_stats() -> dict:
+    out = (C.c_int64 * 5)()
+    lib().fusedmm_b200_jit_stats(out)
+    return dict(zip(("compiled", "disk_hits", "launches", "failures", "nvrtc_found"), (int(v) for v in out)))
 
 
 def call_info() -> CallInfo:

@@ -15,6 +15,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <string>
 #include <vector>
 
 // The inspector's result (fusedmm_b200_plan_create): the CSR resident on one device and its split-row list.
@@ -92,18 +93,19 @@ bool launch_stream<double>(int pattern, int G, int NV, int warps, const Params<d
 template <typename T>
 void launch_any(const Params<T> &p, int warps, long long grid, cudaStream_t s)
 {
-   fused_any_kernel<T><<<static_cast<unsigned int>(grid), warps * 32, 0, s>>>(p);
+   launch_kernel<T>(fused_any_kernel<T>, grid, warps * 32, s, p);
 }
 template <typename T>
 void launch_fixup(const Params<T> &p, long long grid, cudaStream_t s)
 {
-   hub_fixup_kernel<T><<<static_cast<unsigned int>(grid), WARPS_PER_CTA * 32, 0, s>>>(p);
+   launch_kernel<T>(hub_fixup_kernel<T>, grid, WARPS_PER_CTA * 32, s, p);
 }
 
 __global__ void scan_hub_rows(const void *pntrb, const void *pntre, int ptr64, long long m,
                               long long chunk, unsigned long long *counter, long long *hub_row,
                               long long *hub_base, long long hub_cap)
 {
+   grid_launch_dependents();  // the chunk launch that follows may become resident while this scan runs
    const long long r = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
    if (r >= m) return;
    const long long deg = ld_index(pntre, r, ptr64) - ld_index(pntrb, r, ptr64);
@@ -186,7 +188,7 @@ struct DeviceCtx {
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0, multi_skip_empty_rows = 1;
+           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1;
 };
 
 std::mutex g_mu;
@@ -440,6 +442,14 @@ void tiling_for_generic(int G, int NV, int *U)
    else if (G == 32 && NV == 2 && *U == 4) *U = 4 | (3 << 8);
    else if (G == 16 && NV == 2 && *U == 8) *U = 4;
 }
+// Register budget of a kernel built at run time.  For three tilings the offline compiler settles on 80 registers
+// (with a few spilled values) without being asked to, and the tilings were tuned with that; NVRTC gives the same
+// source 96-106 registers, one resident block fewer per SM.  Ask for the 80-register budget explicitly there.
+int jit_budget(int G, int NV, int U, int MB)
+{
+   if (MB == 0 && ((G == 32 && NV == 2 && U == 4) || (G == 32 && NV == 1 && U == 8) || (G == 16 && NV == 1 && U == 8))) return 3;
+   return MB;
+}
 // U of the default instantiation of a (G, NV) tiling
 int default_u(int G, int NV)
 {
@@ -645,6 +655,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    for (int i = 0; i < p.n_peers; i++) vec_ok = vec_ok && aligned16(p.z_peer[i]);
    if (p.z_mc) vec_ok = vec_ok && aligned16(p.z_mc);
    int G = 0, NV = 0, U = 0;
+   int Us = 0;  // gathers in flight and register budget of a kernel specialised for the message (U is the flag-interpreting kernel's)
    const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
    if (vec_ok) {
       if (g_opt.force_tiling) {
@@ -655,8 +666,10 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          U |= static_cast<int>((g_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
       } else {
          choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
+         Us = U;
          if (g_opt.force_generic || d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
       }
+      if (Us == 0) Us = U;
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
@@ -670,6 +683,20 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       if (Gr == 0 || 32 % Gr != 0 || static_cast<long long>(Gr) * NVr * W < a.k) return FUSEDMM_B200_ERR_ARG;
    }
    const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
+   // A message without a built-in specialised kernel gets one built at run time (fusedmm_jit.cu) when the policy of
+   // option "jit" says it is worth it; otherwise, or when that fails, the flag-interpreting instantiation runs.
+   const int jit_policy = ((d.pattern == PAT_GENERIC && !g_opt.force_generic) || g_opt.force_generic == 2) ? static_cast<int>(g_opt.jit) : 0;
+   const long long jit_weight = a.nnz > 0 && a.nnz < (1ll << 40) ? a.nnz * a.k : 0;
+   bool jit_used = false;
+   auto launch_main = [&](const Params<T> &q, int g, int nv, int u_rt, int u_special, int w, long long grid, cudaStream_t s) -> bool {
+      if (jit_policy > 0 && jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_special & 0xFF,
+                                              jit_budget(g, nv, u_special & 0xFF, u_special >> 8), w, q, grid, s, jit_policy,
+                                              jit_weight)) {
+         jit_used = true;
+         return true;
+      }
+      return launch_vec<T>(pattern, g, nv, u_rt, w, q, grid, s);
+   };
 
    int launches = 0;
    bool z_returned = false;  // the blocked path below has already copied Z back to the host
@@ -770,35 +797,41 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // before `st` continues.
    auto enqueue_pass = [&](Params<T> &q, bool with_rows, bool timing) -> int {
       const long long qgrid = (q.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
-      if (!a.plan) {  // a plan carries the result of this scan
-         CK(cudaMemsetAsync(q.counter, 0, sizeof(unsigned long long), st));
-         scan_hub_rows<<<static_cast<unsigned int>((q.m + 255) / 256), 256, 0, st>>>(
-            q.pntrb, q.pntre, q.ptr64, q.m, q.chunk, q.counter, q.hub_row, q.hub_base, q.hub_cap);
-         launches++;
-      }
+      // The whole rows need nothing from the scan, so they start at once on `st`; the scan, the chunks of the split
+      // rows and the fix-up form a chain on the side stream, each launched so that it can become resident while its
+      // predecessor drains (programmatic dependent launch).
       if (timing) CK(cudaEventRecord(c.evk[0], st));
       CK(cudaEventRecord(c.ev_fork, st));
       cudaStream_t side = !g_opt.side_stream ? st : (g_opt.side_priority ? c.side_hi : c.side);
-      auto rows_launch = [&]() -> int {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
-         if (!with_rows) return 0;
-         q.mode = MODE_ROWS;
-         if (vec_ok) { if (!launch_vec<T>(pattern, Gr, NVr, Ur, warps, q, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
-         else launch_any<T>(q, warps, qgrid, st);
-         launches++;
-         return 0;
-      };
       CK(cudaStreamWaitEvent(side, c.ev_fork, 0));
-      if (timing) CK(cudaEventRecord(c.evk[2], side));
+      const bool pdl = g_opt.pdl != 0;
+      if (!a.plan) {  // a plan carries the result of this scan
+         CK(cudaMemsetAsync(q.counter, 0, sizeof(unsigned long long), side));
+         scan_hub_rows<<<static_cast<unsigned int>((q.m + 255) / 256), 256, 0, side>>>(
+            q.pntrb, q.pntre, q.ptr64, q.m, q.chunk, q.counter, q.hub_row, q.hub_base, q.hub_cap);
+         launches++;
+      }
+      // events between the kernels of the chain (option timing_detail) would undo the pairing of the launches
+      const bool detail = timing && g_opt.timing_detail;
+      if (detail) CK(cudaEventRecord(c.evk[2], side));
       q.mode = MODE_HUB_CHUNKS;
-      if (vec_ok) { if (!launch_vec<T>(pattern, G, NV, U, WARPS_PER_CTA, q, hub_grid, side)) return FUSEDMM_B200_ERR_ARG; }
+      q.pdl = pdl && !a.plan && !detail;
+      if (vec_ok) { if (!launch_main(q, G, NV, U, Us, WARPS_PER_CTA, hub_grid, side)) return FUSEDMM_B200_ERR_ARG; }
       else launch_any<T>(q, WARPS_PER_CTA, hub_grid, side);
-      if (timing) CK(cudaEventRecord(c.evk[3], side));
+      if (detail) CK(cudaEventRecord(c.evk[3], side));
+      q.pdl = pdl && !detail;
       launch_fixup<T>(q, c.sm_count, side);
-      if (timing) CK(cudaEventRecord(c.ev_side_end, side));
+      q.pdl = 0;
+      if (detail) CK(cudaEventRecord(c.ev_side_end, side));
       CK(cudaEventRecord(c.ev_join, side));
       launches += 2;
-      if (int e = rows_launch()) return e;
-      if (timing) CK(cudaEventRecord(c.evk[1], st));
+      if (with_rows) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
+         q.mode = MODE_ROWS;
+         if (vec_ok) { if (!launch_main(q, Gr, NVr, Ur, g_opt.force_tiling_rows ? Ur : Us, warps, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
+         else launch_any<T>(q, warps, qgrid, st);
+         launches++;
+      }
+      if (detail) CK(cudaEventRecord(c.evk[1], st));
       CK(cudaStreamWaitEvent(st, c.ev_join, 0));
       CK(cudaGetLastError());
       return 0;
@@ -898,10 +931,12 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       float t = 0.f;
       CK(cudaEventElapsedTime(&t, c.ev0, c.ev1));
       ms += t;
-      CK(cudaEventElapsedTime(&t, c.ev0, c.evk[0])); ms_k[0] += t;
-      CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;
-      CK(cudaEventElapsedTime(&t, c.evk[2], c.evk[3])); ms_k[2] += t;
-      CK(cudaEventElapsedTime(&t, c.evk[3], c.ev_side_end)); ms_k[3] += t;
+      if (g_opt.timing_detail) {
+         CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[2])); ms_k[0] += t;   // start of the pass -> scan done
+         CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;   // whole rows, beside the chain
+         CK(cudaEventElapsedTime(&t, c.evk[2], c.evk[3])); ms_k[2] += t;
+         CK(cudaEventElapsedTime(&t, c.evk[3], c.ev_side_end)); ms_k[3] += t;
+      }
       CK(cudaEventElapsedTime(&t, c.evk[0], c.ev1)); ms_main += t;
       nh = static_cast<long long>(packed >> HUB_SHIFT);
       nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
@@ -936,6 +971,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    t_info.ms_scan = ms_k[0]; t_info.ms_rows = ms_k[1]; t_info.ms_chunks = ms_k[2]; t_info.ms_fixup = ms_k[3];
    t_info.ms_main = ms_main;
    t_info.sop_kind = d.sop == OP_UDEF ? sopk.kind : -1;
+   t_info.jit_kernel = jit_used ? 1 : 0;
    static const bool trace = getenv("FUSEDMM_B200_TRACE") != nullptr;
    if (trace)
       fprintf(stderr, "fusedmm_b200: msg=%#x %s m=%lld k=%lld engine=%d tiling=%dx%d launches=%d split_rows=%lld chunks=%lld "
@@ -1347,6 +1383,31 @@ int fusedmm_b200_zero_empty_rows(int32_t dtype, int32_t ptr_bits, int64_t m, int
    return 0;
 }
 
+int fusedmm_b200_jit_prepare(int32_t dtype, int32_t imessage, int64_t k)
+{
+   std::lock_guard<std::mutex> lock(g_mu);
+   if ((dtype != 0 && dtype != 1) || k <= 0) return FUSEDMM_B200_ERR_ARG;
+   Decoded d;
+   int st = decode_message(imessage, g_opt, &d);
+   if (st) return st;
+   if (d.pattern != PAT_GENERIC || d.aop == AOP_NOOP) return 0;  // built in, or nothing to compute
+   const int W = dtype == 0 ? 4 : 2;
+   if (k % W != 0) return 0;                                      // the element-strided kernels take it
+   int G = 0, NV = 0, U = 0;
+   choose_tiling(k / W, dtype == 1, &G, &NV, &U);
+   if (G == 0) return 0;
+   return jit_prepare(dtype, d.vop, d.rop, d.vsc, d.aop, G, NV, U & 0xFF, jit_budget(G, NV, U & 0xFF, U >> 8)) == 0 ? 0 : FUSEDMM_B200_ERR_NO_OPT;
+}
+
+int fusedmm_b200_jit_stats(int64_t *out)
+{
+   if (!out) return FUSEDMM_B200_ERR_ARG;
+   std::lock_guard<std::mutex> lock(g_mu);
+   const JitStats s = jit_stats();
+   out[0] = s.compiled; out[1] = s.disk_hits; out[2] = s.launches; out[3] = s.failures; out[4] = s.nvrtc_found;
+   return 0;
+}
+
 int fusedmm_b200_set_sop(int32_t kind, double p0, double p1, double p2)
 {
    if (kind < 0 || kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_ARG;
@@ -1606,18 +1667,47 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "strict_udef")) return &g_opt.strict_udef;
    if (!strcmp(name, "multi_skip_empty_rows")) return &g_opt.multi_skip_empty_rows;
+   if (!strcmp(name, "jit")) return &g_opt.jit;
+   if (!strcmp(name, "pdl")) return &g_opt.pdl;
+   if (!strcmp(name, "timing_detail")) return &g_opt.timing_detail;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
 }
+// FUSEDMM_B200_OPTIONS="name=value,name=value": options set from the environment when the library is loaded, for
+// programs that cannot be changed to call fusedmm_b200_set_option (unknown names and malformed items are ignored).
+static struct EnvOptions {
+   EnvOptions()
+   {
+      const char *e = getenv("FUSEDMM_B200_OPTIONS");
+      if (!e) return;
+      std::string all(e);
+      size_t pos = 0;
+      while (pos < all.size()) {
+         size_t end = all.find(',', pos);
+         if (end == std::string::npos) end = all.size();
+         const std::string item = all.substr(pos, end - pos);
+         const size_t eq = item.find('=');
+         if (eq != std::string::npos) {
+            int64_t *slot = option_slot(item.substr(0, eq).c_str());
+            char *rest = nullptr;
+            const long long v = strtoll(item.c_str() + eq + 1, &rest, 10);
+            if (slot && rest && *rest == '\0' && v >= 0) *slot = v;
+         }
+         pos = end + 1;
+      }
+   }
+} g_env_options;
+
 int fusedmm_b200_set_option(const char *name, int64_t value)
 {
    std::lock_guard<std::mutex> lock(g_mu);
    int64_t *s = option_slot(name);
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.force_generic || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.force_generic && value > 2) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
-   if (s == &g_opt.engine && value > 2) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.engine || s == &g_opt.jit) && value > 2) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.chunk_ctas_per_sm && (value < 1 || value > 64)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.edge_quantum && (value < 32 || value > (1ll << 24))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.stream_depth && (value < 1 || value > 32)) return FUSEDMM_B200_ERR_ARG;

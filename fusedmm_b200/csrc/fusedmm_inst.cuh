@@ -25,8 +25,8 @@ namespace fmm {
 
 #define FMM_TILING_CASE(G_, NV_, U_, MB_)                                                            \
    case ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                                           \
-      fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_>                              \
-         <<<static_cast<unsigned int>(grid), warps * 32, 0, stream>>>(p);                             \
+      launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_>, grid,      \
+                        warps * 32, stream, p);                                                       \
       return true;
 
 // persistent launch of the edge-stream kernel: as many CTAs as fit on the device at once

@@ -20,9 +20,15 @@
 //   * rows longer than `chunk` edges are cut into chunks that other warps process; their partial
 //     sums go to a scratch buffer and a small second kernel adds them in chunk order, so the result
 //     does not depend on scheduling (no floating-point atomics).
+// This file is also the source the library hands to NVRTC at run time to build message-specific kernels
+// (fusedmm_jit.cu), so it includes nothing else when compiled that way.
 #pragma once
+#ifndef __CUDACC_RTC__
 #include <cuda_runtime.h>
 #include <stdint.h>
+#else
+typedef unsigned long long uintptr_t;
+#endif
 
 namespace fmm {
 
@@ -86,6 +92,9 @@ struct Params {
    // 1: rows without edges are not sent to the other GPUs (every GPU holds the row pointers and zeroes, or
    // keeps, those rows of its own copy itself: zero_empty_rows_kernel); their result is stored locally only
    int skip_empty_remote;
+   // host side only: launch this kernel with programmatic stream serialization (it may become resident while the
+   // kernel before it in the stream is still running and waits at grid_dependency_wait for that kernel's results)
+   int pdl;
 };
 
 // ---------------------------------------------------------------------------------------------------
@@ -166,6 +175,13 @@ __device__ __forceinline__ void st_multicast(double *mc, double v)
 {
    asm volatile("multimem.st.relaxed.sys.global.f64 [%0], %1;" ::"l"(mc), "d"(v) : "memory");
 }
+
+// Programmatic dependent launch: a kernel launched with programmatic stream serialization must not touch what the
+// kernel before it in the stream produces until this returns; without that launch attribute it is a no-op.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel in the stream (if it was launched that way) become resident now instead of when this grid
+// has drained; it still waits for this grid's completion in grid_dependency_wait.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
 template <typename T> __device__ __forceinline__ T pos_inf();
 template <> __device__ __forceinline__ float  pos_inf<float>()  { return __int_as_float(0x7f800000); }
@@ -352,6 +368,45 @@ __device__ __forceinline__ bool chunk_item(const Params<T> &p, long long item, l
    return true;
 }
 
+// Z_row = AOP(old Z_row or identity, partial_0, partial_1, ...) in chunk order, by one warp; also sends the row to
+// the other GPUs when the call asks for that.  Lane l owns elements l, l+32, ... of a 128-element tile of K; the
+// loads of four chunks are in flight together while the additions keep their order.
+template <typename T>
+__device__ __forceinline__ void reduce_hub_row(const Params<T> &p, long long row, long long base, long long nch, int lane)
+{
+   constexpr int EPT = 4;
+   T *zr = p.z + row * p.ldz;
+   for (long long kt = 0; kt < p.k; kt += 32 * EPT) {
+      T a[EPT];
+#pragma unroll
+      for (int e = 0; e < EPT; e++) {
+         const long long t = kt + e * 32 + lane;
+         a[e] = (p.accumulate && t < p.k) ? zr[t] : aop_identity<T>(p.aop);
+      }
+      const T *src = p.partials + base * p.k + kt + lane;
+#pragma unroll 4
+      for (long long q = 0; q < nch; q++, src += p.k) {
+         T v[EPT];
+#pragma unroll
+         for (int e = 0; e < EPT; e++) v[e] = (kt + e * 32 + lane < p.k) ? __ldcg(src + e * 32) : aop_identity<T>(p.aop);
+#pragma unroll
+         for (int e = 0; e < EPT; e++) a[e] = aop_apply(p.aop, a[e], v[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < EPT; e++) {
+         const long long t = kt + e * 32 + lane;
+         if (t < p.k) {
+            if (p.z_mc) {
+               st_multicast(p.z_mc + row * p.ldz + t, a[e]);
+            } else {
+               zr[t] = a[e];
+               for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = a[e];
+            }
+         }
+      }
+   }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // Vector engine: one warp, one work item, K <= G*NV*W elements, everything 16-byte aligned.
 // ---------------------------------------------------------------------------------------------------
@@ -527,6 +582,7 @@ fused_vec_kernel(const Params<T> p)
    const long long stride = static_cast<long long>(gridDim.x) * wpc;
    long long nh = 0, nchunks = 0;
    if (p.mode == MODE_HUB_CHUNKS) {
+      grid_dependency_wait();  // the split-row list comes from the scan that precedes this launch
       const unsigned long long c = *p.counter;
       nh = static_cast<long long>(c >> HUB_SHIFT);
       nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
@@ -641,6 +697,7 @@ fused_any_kernel(const Params<T> p)
    const long long stride = static_cast<long long>(gridDim.x) * wpc;
    long long nh = 0, nchunks = 0;
    if (p.mode == MODE_HUB_CHUNKS) {
+      grid_dependency_wait();
       const unsigned long long c = *p.counter;
       nh = static_cast<long long>(c >> HUB_SHIFT);
       nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
@@ -736,6 +793,7 @@ __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 hub_fixup_kernel(const Params<T> p)
 {
    const int lane = threadIdx.x & 31;
+   grid_dependency_wait();  // the partial sums come from the chunk launch that precedes this one
    const unsigned long long c = *p.counter;
    const long long nh = static_cast<long long>(c >> HUB_SHIFT);
    const long long nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
@@ -746,18 +804,7 @@ hub_fixup_kernel(const Params<T> p)
         slot += stride) {
       const long long row = p.hub_row[slot], base = p.hub_base[slot];
       const long long deg = ld_index(p.pntre, row, p.ptr64) - ld_index(p.pntrb, row, p.ptr64);
-      const long long nch = (deg + p.chunk - 1) / p.chunk;
-      T *zr = p.z + row * p.ldz;
-      for (long long t = lane; t < p.k; t += 32) {
-         T a = p.accumulate ? zr[t] : aop_identity<T>(p.aop);
-         for (long long q = 0; q < nch; q++) a = aop_apply(p.aop, a, p.partials[(base + q) * p.k + t]);
-         if (p.z_mc) {
-            st_multicast(p.z_mc + row * p.ldz + t, a);
-         } else {
-            zr[t] = a;
-            for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = a;
-         }
-      }
+      reduce_hub_row(p, row, base, (deg + p.chunk - 1) / p.chunk, lane);
    }
 }
 
@@ -791,6 +838,23 @@ zero_empty_rows_kernel(const void *pntrb, const void *pntre, int ptr64, long lon
 // Host-side launch table (defined in the per-pattern translation units).
 // ---------------------------------------------------------------------------------------------------
 enum : int { PAT_GENERIC = 0, PAT_SIGMOID = 1, PAT_TDIST = 2, PAT_SPMM = 3, PAT_GCN = 4 };
+#ifndef __CUDACC_RTC__
+// <<<grid, block, 0, stream>>> with, when p.pdl is set, the attribute that lets the kernel overlap its launch with
+// the tail of the kernel before it in the stream.
+template <typename T>
+inline cudaError_t launch_kernel(void (*kern)(const Params<T>), long long grid, int threads, cudaStream_t stream, const Params<T> &p)
+{
+   cudaLaunchConfig_t cfg = {};
+   cfg.gridDim = dim3(static_cast<unsigned int>(grid));
+   cfg.blockDim = dim3(threads);
+   cfg.stream = stream;
+   cudaLaunchAttribute attr[1];
+   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+   attr[0].val.programmaticStreamSerializationAllowed = 1;
+   cfg.attrs = attr;
+   cfg.numAttrs = p.pdl ? 1 : 0;
+   return cudaLaunchKernelEx(&cfg, kern, p);
+}
 
 // Launches fused_vec_kernel<T, pattern ops, G, NV, U> with `grid` CTAs on `stream`.
 // Returns false when that (G, NV) tiling is not instantiated.
@@ -800,5 +864,18 @@ template <typename T>
 void launch_any(const Params<T> &p, int warps, long long grid, cudaStream_t stream);
 template <typename T>
 void launch_fixup(const Params<T> &p, long long grid, cudaStream_t stream);
+
+// Message-specific kernels built at run time (fusedmm_jit.cu): launches fused_vec_kernel<T, vop, rop, vsc, aop, G,
+// NV, U, MB> compiled by NVRTC for exactly this message.  Returns false when there is no such kernel (NVRTC not
+// found, compilation failed, the policy says this message is not worth compiling yet): the caller then launches the
+// flag-interpreting instantiation.  `weight` is the size of the call (edges x K, 0 if unknown) for that policy.
+template <typename T>
+bool jit_launch_vec(int vop, int rop, int vsc, int aop, int G, int NV, int U, int MB, int warps, const Params<T> &p,
+                    long long grid, cudaStream_t stream, int policy, long long weight);
+// Compile (or find in the cache) without launching; 0 on success.  Works without a GPU.
+int jit_prepare(int is_double, int vop, int rop, int vsc, int aop, int G, int NV, int U, int MB);
+struct JitStats { long long compiled, disk_hits, launches, failures; int nvrtc_found; };
+JitStats jit_stats();
+#endif
 
 }  // namespace fmm

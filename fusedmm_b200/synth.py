@@ -197,9 +197,15 @@ def make_config(name, device="cpu", dtype=torch.float32, scale=None, ptr_dtype=t
 
 
 def algorithmic_bytes(msg, nnz, m, k, val_bytes, idx_bytes, ptr_bytes, beta_nonzero=False):
-    """Bytes one call must move: every gathered Y row in full, one column id (and one edge value for
-    SpMM) per edge, X_u read (messages that use X) and Z_u written once per row, two row pointers per row."""
-    reads_x = msg in (M.MSG_SIGMOID, M.MSG_TDIST)
-    per_edge = k * val_bytes + idx_bytes + (val_bytes if msg == M.MSG_SPMM else 0)
-    r = (2 if reads_x else 1) + (1 if beta_nonzero else 0)
+    """Bytes one call must move: every gathered Y row in full, one column id (and one edge value when the
+    message consumes it: ROP_NOOP with a VSC stage, e.g. SpMM) per edge, X_u read (messages whose VOP or ROP uses
+    X) and Z_u written once per row (and read when the call accumulates: beta != 0, or any message outside the
+    four optimised patterns), two row pointers per row."""
+    vop, rop, vsc = msg & 0xF, msg & 0xF0, msg & 0xF000
+    reads_x = vop not in (M.VOP_COPY_RHS, M.VOP_NOOP) or rop in (M.ROP_DOT, M.ROP_ADD_LHS, M.ROP_NORML)
+    reads_y = vop != M.VOP_COPY_LHS
+    uses_val = rop == M.ROP_NOOP and vsc != M.VSC_NOOP
+    accumulates = beta_nonzero or msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
+    per_edge = (k * val_bytes + idx_bytes if reads_y else 0) + (val_bytes if uses_val else 0)
+    r = (2 if reads_x else 1) + (1 if accumulates else 0)
     return nnz * per_edge + m * (r * k * val_bytes + 2 * ptr_bytes)

@@ -367,7 +367,25 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *   "side_stream"    1 (default): the chunks of split rows run on a second stream beside the whole rows;
  *                    0: every launch on one stream (12 % slower on the benchmark graph; diagnostic).
  *   "force_tiling_rows"  as force_tiling, for the whole-row launch only (0 = the call's tiling).
- *   "force_generic"  1 = run every message through the flag-interpreting kernel.
+ *   "force_generic"  1 = run every message through the flag-interpreting kernel; 2 = treat the four built-in
+ *                    patterns like any other message (flag-interpreting kernel, or a run-time-built one as option
+ *                    "jit" decides): diagnostics.
+ *   "jit"            what a message outside the four built-in patterns runs on.  The reference has optimised
+ *                    kernels for four messages and a function-pointer loop for the rest (fusedMM.c:512-605,
+ *                    :698-739; its TODO :516-518 asks for generated kernels for "all vector ops").  Here the
+ *                    kernel template is instantiated for the message at hand at run time with NVRTC, cached in
+ *                    the process and as a cubin under $FUSEDMM_B200_JIT_CACHE (default ~/.cache/fusedmm_b200;
+ *                    empty = no files).  1 (default): build it once the same message and K class has been
+ *                    launched 16 times (8 calls), or at once when nnz * k >= 2^26 (about a second, once per
+ *                    machine); until then, and if NVRTC (libnvrtc.so.12, or $FUSEDMM_B200_NVRTC) is missing, the
+ *                    flag-interpreting kernel runs, which is 1.7-2.2x slower.  0: never build.  2: build on first
+ *                    use.  fusedmm_b200_jit_prepare builds ahead of time.
+ *   "pdl"            1 (default): the chain scan -> chunks of split rows -> fix-up is launched with programmatic
+ *                    stream serialization, so each kernel becomes resident while its predecessor drains (what
+ *                    matters for small graphs, where launch gaps are a tenth of the call); 0: plain launches.
+ *   "timing_detail"  1 (default): a synchronous call records an event after each launch (the ms_* fields of
+ *                    fusedmm_b200_call_info); those records sit between the kernels of the chain and undo "pdl"
+ *                    for that call.  0: only ms_main and device_ms are measured, the launches stay paired.
  *   "multi_skip_empty_rows"  1 (default): fusedmm_b200_csr_multi does not send rows without edges to the other
  *                    GPUs (see there); 0: every row of the shard is sent.
  *   "strict_udef"    0 (default): a host SOP_UDEF_FUNC handed to a *_udef entry point is evaluated at 25 sample
@@ -379,7 +397,8 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    with FUSEDMM_B200_ERR_NOMEM (host-side fault injection for tests; nothing is
  *                    done to the GPU).
  * fusedmm_b200_get_option(name, &value) reads them back.
- * Environment: FUSEDMM_B200_TRACE (any value) prints one line per call to stderr: message, sizes,
+ * Environment: FUSEDMM_B200_OPTIONS="name=value,name=value" sets options when the library is loaded (for
+ * programs that cannot be changed to call fusedmm_b200_set_option); FUSEDMM_B200_TRACE (any value) prints one line per call to stderr: message, sizes,
  * engine and tiling, launches, split rows, bytes copied and the CUDA-event times of the launches.
  * ---------------------------------------------------------------------------------------------- */
 int fusedmm_b200_set_option(const char *name, int64_t value);
@@ -398,15 +417,27 @@ typedef struct fusedmm_b200_call_info {
    float   device_ms;         /* CUDA-event time of the kernels of a synchronous call        */
    int32_t sop_kind;          /* SOP that ran                                                */
    /* CUDA-event time of each launch of a synchronous call, in launch order */
-   float   ms_scan;           /* scan_hub_rows: finds the rows to split                      */
+   float   ms_scan;           /* scan_hub_rows: finds the rows to split (from the start of the call) */
    float   ms_rows;           /* main kernel, one warp per whole row                         */
    float   ms_chunks;         /* main kernel over the chunks of split rows                   */
    float   ms_fixup;          /* hub_fixup_kernel: adds the chunk partials into Z            */
    int32_t engine;            /* 1 = row scheduler, 2 = edge-stream scheduler                */
-   float   ms_main;           /* from the end of the scan to the end of the last main-kernel /
-                                 fix-up launch (the whole-row and the chunk launches overlap)  */
+   float   ms_main;           /* from the first launch of the call to the end of its last one: the whole-row
+                                 launch runs beside the chain scan -> chunks -> fix-up             */
+   int32_t jit_kernel;        /* 1: the main kernel was one built at run time for this message */
 } fusedmm_b200_call_info;
 int fusedmm_b200_last_call_info(fusedmm_b200_call_info *out);
+
+/* Builds (or finds in the cache) the kernel specialised for `imessage` at feature length k and value type
+ * dtype (0 float, 1 double) without running anything, so that the first real call does not pay for the
+ * compilation; needs no GPU.  0 on success or when the message needs no such kernel (built-in pattern,
+ * k not a multiple of 16 bytes); FUSEDMM_B200_ERR_NO_OPT when NVRTC is missing or the build failed; the
+ * reference's status codes for an invalid message.  No counterpart in the reference, whose kernels are
+ * generated at build time (kernels/CONFIG/rungen.top).
+ * fusedmm_b200_jit_stats: out[0..4] = kernels compiled by this process, found in the file cache, launches of
+ * run-time-built kernels, failures, NVRTC found (0/1). */
+int fusedmm_b200_jit_prepare(int32_t dtype, int32_t imessage, int64_t k);
+int fusedmm_b200_jit_stats(int64_t *out);
 
 const char *fusedmm_b200_status_string(int status);
 const char *fusedmm_b200_version(void);

@@ -4,6 +4,7 @@ reference's status codes before any CUDA call, and the nnz-balanced row sharding
 import ctypes
 import re
 import subprocess
+import sys
 from pathlib import Path
 
 import numpy as np
@@ -92,6 +93,30 @@ def test_kernels_header_compiles_as_c_and_cxx_for_both_index_types(tmp_path):
                                 f"-L{libdir}", "-lfusedmm_b200", f"-Wl,-rpath,{libdir}", "-o", str(exe)], check=True)
                 run = subprocess.run([str(exe)], check=True, capture_output=True, text=True)
                 assert "done" in run.stdout and run.stderr.count("Kernel not implemented yet!!!") == 3
+
+
+def test_kernels_for_other_messages_can_be_built_ahead_of_time_without_a_gpu(lib, tmp_path, monkeypatch):
+    """fusedmm_b200_jit_prepare compiles the kernel specialised for a message with NVRTC and files the cubin; a
+    second request is answered from the process, a new process from the file."""
+    monkeypatch.setenv("FUSEDMM_B200_JIT_CACHE", str(tmp_path))
+    msg = M.VOP_MIN | M.ROP_ADD_RHS | M.SOP_COPY | M.VSC_ADD | M.AOP_MIN
+    before = api.jit_stats()
+    assert api.jit_prepare(msg, 96, np.float32) == 0
+    assert api.jit_prepare(msg, 96, np.float32) == 0
+    assert api.jit_prepare(msg, 24, np.float64) == 0
+    after = api.jit_stats()
+    assert after["nvrtc_found"] == 1 and after["compiled"] - before["compiled"] == 2 and after["failures"] == before["failures"]
+    files = sorted(tmp_path.glob("sm100a_*.cubin"))
+    assert len(files) == 2 and all(f.stat().st_size > 10_000 for f in files)
+    assert b"fused_vec_kernel" in files[0].read_bytes()[:400]    # first line: the kernel's mangled name
+    # nothing to build: a built-in pattern, K not a multiple of 16 bytes; an invalid message keeps its status
+    assert api.jit_prepare(M.MSG_TDIST, 128) == 0 and api.jit_prepare(msg, 7) == 0
+    assert api.jit_prepare(0x11F18, 128) == M.ERR_VOP
+    assert api.jit_stats()["compiled"] == after["compiled"]
+    code = ("import sys; sys.path.insert(0, %r); import numpy as np; from fusedmm_b200 import api; "
+            "assert api.jit_prepare(%d, 96, np.float32) == 0; s = api.jit_stats(); "
+            "assert s['disk_hits'] == 1 and s['compiled'] == 0, s" % (str(ROOT), msg))
+    subprocess.run([sys.executable, "-c", code], check=True)
 
 
 def test_named_messages():

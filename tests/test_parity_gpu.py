@@ -375,7 +375,83 @@ def test_peer_stores_replicate_finished_rows(cuda_device, oracle):
         oracle.csr(M.MSG_TDIST, m - r0, n, k, val, indx, pntrb[r0:].copy(), pntre[r0:].copy(), x[r0:], k, y, k, 0.0,
                    want[r0:], k, sop_kind=M.SOP_TDIST)
         assert rel_err(zs[0].cpu().numpy(), want) <= 1e-4
+        # rows without edges are not sent: a peer zeroes them in its own copy from the row pointers
+        empty = torch.from_numpy(pntre[r0:] <= pntrb[r0:]).to(cuda_device)
+        assert bool(empty.any()) and bool((zs[1][r0:][empty] == 5.0).all()) and bool((zs[0][r0:][empty] == 0.0).all())
+        assert torch.equal(zs[0][r0:][~empty], zs[1][r0:][~empty])
+        for peer in zs[1:]:
+            assert api.zero_empty_rows(t[2][r0:], t[3][r0:], peer[r0:], k, k) == 0
+        torch.cuda.synchronize()
         assert torch.equal(zs[0], zs[1]) and torch.equal(zs[0], zs[2])
+        # option multi_skip_empty_rows = 0: every row of the shard is sent
+        zs = [torch.full((m, k), 5.0, device=cuda_device) for _ in range(2)]
+        api.set_option("multi_skip_empty_rows", 0)
+        try:
+            st = api.fusedMM_csr(M.MSG_TDIST, m - r0, n, k, 1.0, 0, m, n, t[0], t[1], t[2][r0:], t[3][r0:], t[4][r0:],
+                                 k, t[5], k, 0.0, zs[0][r0:], k, sop=M.SOP_TDIST, z_peers=[zs[1][r0:].data_ptr()])
+        finally:
+            api.set_option("multi_skip_empty_rows", 1)
+        torch.cuda.synchronize()
+        assert st == 0 and torch.equal(zs[0], zs[1]) and rel_err(zs[0].cpu().numpy(), want) <= 1e-4
+
+
+def test_run_time_built_kernels_for_messages_without_a_built_in_one(cuda_device, oracle, tmp_path, monkeypatch):
+    """Messages outside the four optimised patterns get a kernel specialised for them, built at run time with NVRTC
+    (option jit = 2: on first use).  Its result must agree with the flag-interpreting kernel's and with the oracle
+    within the tolerance; the cubin is found in the file cache afterwards."""
+    import torch
+    monkeypatch.setenv("FUSEDMM_B200_JIT_CACHE", str(tmp_path / "jit"))
+    before = api.jit_stats()
+    rng = np.random.default_rng(123)
+    m, n = 1200, 1000
+    names = ["subl_norml_udef_mul_max", "add_addrhs_vscadd_add", "max_dot_copy_mul_min", "min_noop_copy_vscadd_max",
+             "copylhs_addlhs_mul_add", "subr_normr_noopsop_noopvsc_add"]
+    try:
+        for vt in (np.float32, np.float64):
+            for k in (32, 128, 256):
+                pntrb, pntre, indx, val = random_csr(rng, m, n, 9, np.int64, np.int32, hub=1500)
+                val = val.astype(vt)
+                x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+                for name in names[:3] if k != 128 else names:
+                    msg, sop = MESSAGES[name], sop_for(name)
+                    z0 = rng.uniform(-1, 1, size=(m, k)).astype(vt)
+                    want = z0.copy()
+                    assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop,
+                                      zero_first=False) == 0
+                    api.set_option("jit", 0)
+                    st0, z_rt = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0.copy(), k, sop=sop)
+                    assert st0 == 0 and api.call_info().jit_kernel == 0
+                    api.set_option("jit", 2)
+                    st1, z_jit = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0.copy(), k, sop=sop)
+                    info = api.call_info()
+                    assert st1 == 0 and info.jit_kernel == 1 and info.hub_rows >= 1, (name, k, vt)
+
+                    def exact():
+                        if vt == np.float32:
+                            ex = z0.astype(np.float64)
+                            oracle.csr(msg, m, n, k, val.astype(np.float64), indx, pntrb, pntre, x.astype(np.float64), k,
+                                       y.astype(np.float64), k, 0.0, ex, k, sop_kind=sop, zero_first=False)
+                            return ex
+                        from oracle.cpu import numpy_fusedmm
+                        return numpy_fusedmm(msg, m, k, val, indx, pntrb, pntre, x, y, z0, sop_kind=sop, dtype=np.longdouble)
+
+                    ok, e, e_gpu, e_or = within_tolerance(z_jit, want, RTOL[np.dtype(vt)], exact)
+                    assert ok, (name, k, vt, e, e_gpu, e_or)
+                    assert rel_err(z_jit, z_rt) <= RTOL[np.dtype(vt)]
+    finally:
+        api.set_option("jit", 1)
+    after = api.jit_stats()
+    assert after["nvrtc_found"] == 1 and after["failures"] == before["failures"]
+    assert after["compiled"] - before["compiled"] >= 18 and after["launches"] > before["launches"]
+    assert len(list((tmp_path / "jit").glob("sm100a_*.cubin"))) == after["compiled"] - before["compiled"]
+    # policy 1 (the default): a small call does not compile anything ...
+    msg = MESSAGES["add_addrhs_vscadd_add"] ^ M.AOP_ADD ^ M.AOP_MAX   # a tuple not used above
+    st, _ = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0.copy(), k)
+    assert st == 0 and api.call_info().jit_kernel == 0 and api.jit_stats()["compiled"] == after["compiled"]
+    # ... until the same message has come 8 times
+    for _ in range(8):
+        st, _ = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0.copy(), k)
+    assert st == 0 and api.call_info().jit_kernel == 1 and api.jit_stats()["compiled"] == after["compiled"] + 1
 
 
 def test_async_stream_entry(cuda_device, oracle):
