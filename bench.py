@@ -228,11 +228,27 @@ def cpu_leg(torch, eng, cfg, csr, x, z_gpu, nnz, flops_per_edge, target_s, steps
 def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n, k, nnz, r0, r1, flops_per_edge, barrier):
     """The same call through the synchronous typed entry point with pinned HOST arrays: all copies inside."""
     e2e_steps = args.e2e_steps or (3 if nnz > 200_000_000 else max(3, min(args.steps, 8)))
-    hv = csr.val.cpu().pin_memory()
-    hi = csr.indx.cpu().pin_memory()
-    hp = csr.rowptr.cpu().pin_memory()
-    hx = x.cpu().pin_memory()
-    hz = torch.zeros((r1 - r0, k), dtype=tdtype).pin_memory()
+
+    def pinned(t):  # straight from the device into pinned memory: no pageable copy in between
+        h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        h.copy_(t)
+        return h
+
+    # every rank of the node holds its own host copy of the inputs: make sure the node has room for all of them
+    need = sum(t.numel() * t.element_size() for t in (csr.val, csr.indx, csr.rowptr, x)) + 2 * (r1 - r0) * k * x.element_size()
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = None
+    fits = torch.tensor([1.0 if avail is None or need * world < 0.6 * avail else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(fits, op=dist.ReduceOp.MIN)
+    if fits.item() == 0.0:
+        return {"value": None, "unit": "GFLOP/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
+                "skipped": f"{world} ranks x {need / 2**30:.1f} GiB of pinned host copies do not fit this node's free memory"}, True
+    hv, hi, hp, hx = pinned(csr.val), pinned(csr.indx), pinned(csr.rowptr), pinned(x)
+    hz = torch.zeros((r1 - r0, k), dtype=tdtype, pin_memory=True)
     hpb, hpe = hp[:-1], hp[1:]
 
     def e2e_step():
@@ -267,7 +283,7 @@ def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n,
     # the same with the graph kept on the device by a plan (inspector/executor split): per step only X(=Y) goes
     # in and Z comes out; reported beside the headline figure, which stays the plain fusedMM_csr call
     plan = api.Plan(hi, hpb[r0:r1], hpe[r0:r1], hv)  # this rank's rows
-    hz2 = torch.zeros((r1 - r0, k), dtype=tdtype).pin_memory()
+    hz2 = torch.zeros((r1 - r0, k), dtype=tdtype, pin_memory=True)
 
     def plan_step():
         st = plan.csr(msg, n, k, hx[r0:], k, hx, k, 0.0, hz2, k, sop=sop if sop is not None else 0)

@@ -188,7 +188,7 @@ struct DeviceCtx {
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1;
+           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0;
 };
 
 std::mutex g_mu;
@@ -431,6 +431,15 @@ void choose_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
    else if (nvec <= 256) { *G = 32; *NV = 8; *U = 1; }
    else { *G = 0; *NV = 0; *U = 0; }
 }
+// The whole-row launch may use other gathers in flight / register budget than the chunk launch: its rows are short
+// (at most `chunk` edges, on R-MAT graphs ten on average), so fewer gathers per slot are outstanding anyway and more
+// resident warps pay more.  K = 128 floats on R-MAT scale 24: 43.7 ms per call with (16, 2, 4) in 80 registers for
+// the whole rows against 45.4 with the chunk launch's (16, 2, 8) in 128.  false: use the chunk launch's tiling.
+bool choose_rows_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
+{
+   if (!is_double && nvec > 16 && nvec <= 32) { *G = 16; *NV = 2; *U = 4 | (3 << 8); return true; }
+   return false;
+}
 // The flag-interpreting kernels need more registers than the specialised ones, so their best register budget and
 // number of gathers in flight differ (B200, float): K = 512 SpMM message 43.8 ms without the 80-register budget of
 // (32, 4, 2) against 52.0 with it; K = 256 FR message 7.24 ms with an 80-register budget on (32, 2, 4) against 8.95
@@ -619,6 +628,9 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // best everywhere else.  nnz is only a hint here (the reference never reads it); a wrong value costs
    // speed, not correctness.
    if (a.nnz > 0 && a.nnz < (1ll << 24) && static_cast<size_t>(a.k) * es <= 1024) p.chunk = std::min<long long>(p.chunk, 128);
+   // below about two million edges the call is a chain of latencies, and the longest whole row is one link of it:
+   // R-MAT scale 14, K = 128, L2 flushed: 55 us per call with rows split at 64 edges, 59 at 128, 80 at 32
+   if (a.nnz > 0 && a.nnz < (1ll << 21) && static_cast<size_t>(a.k) * es <= 1024) p.chunk = std::min<long long>(p.chunk, 64);
    if (a.plan) p.chunk = a.plan->chunk;  // the split-row list of a plan was made for this chunk size
    p.n_peers = 0;
    p.z_mc = nullptr;
@@ -673,29 +685,57 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
-   int Gr = G, NVr = NV, Ur = U;
+   int Gr = G, NVr = NV, Ur = U, Urs = Us;  // Urs: U | budget of a specialised kernel for the whole rows
+   if (vec_ok && !g_opt.force_tiling && !g_opt.force_tiling_rows) {
+      int g2 = 0, nv2 = 0, u2 = 0;
+      if (choose_rows_tiling(a.k / W, sizeof(T) == 8, &g2, &nv2, &u2) && static_cast<long long>(g2) * nv2 * W >= a.k) {
+         if (d.pattern != PAT_GENERIC && !g_opt.force_generic) { Gr = g2; NVr = nv2; Ur = u2; Urs = u2; }
+         else if (g2 == G && nv2 == NV) Urs = u2;  // the flag-interpreting kernel keeps its own; one built for the message takes it
+      }
+   }
    if (vec_ok && g_opt.force_tiling_rows) {
       Gr = static_cast<int>((g_opt.force_tiling_rows >> 8) & 0xFF);
       NVr = static_cast<int>(g_opt.force_tiling_rows & 0xFF);
       Ur = static_cast<int>((g_opt.force_tiling_rows >> 16) & 0xFF);
       if (Ur == 0) Ur = default_u(Gr, NVr);
       Ur |= static_cast<int>((g_opt.force_tiling_rows >> 24) & 0xFF) << 8;
+      Urs = Ur;
       if (Gr == 0 || 32 % Gr != 0 || static_cast<long long>(Gr) * NVr * W < a.k) return FUSEDMM_B200_ERR_ARG;
    }
    const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
    // A message without a built-in specialised kernel gets one built at run time (fusedmm_jit.cu) when the policy of
    // option "jit" says it is worth it; otherwise, or when that fails, the flag-interpreting instantiation runs.
-   const int jit_policy = ((d.pattern == PAT_GENERIC && !g_opt.force_generic) || g_opt.force_generic == 2) ? static_cast<int>(g_opt.jit) : 0;
    const long long jit_weight = a.nnz > 0 && a.nnz < (1ll << 40) ? a.nnz * a.k : 0;
+   int jit_policy = ((d.pattern == PAT_GENERIC && !g_opt.force_generic) || g_opt.force_generic == 2) ? static_cast<int>(g_opt.jit) : 0;
+   // Option "jit_call_shape": a large call of ANY message (the four patterns included) gets a kernel built for the
+   // shape of the call too: exactly this K (no bounds predicates on the vectors of a row) and, when column ids are
+   // 32 bits wide and all of Y lies within 2^32 elements, 32-bit row offsets.
+   int jit_flags = 0;
+   if (vec_ok && g_opt.jit_call_shape && g_opt.jit > 0 && !g_opt.force_generic && (jit_weight >= (1ll << 26) || g_opt.jit_call_shape == 2)) {
+      if (static_cast<long long>(G) * NV * W == a.k) jit_flags |= FLAG_EXACT_K;
+      const bool need_y_ = vop_reads_y(d.vop);
+      if (need_y_ && a.idx_bits == 32 && a.n > 0 && static_cast<double>(a.n - 1) * static_cast<double>(a.ldy) + static_cast<double>(a.k) <= 4294967295.0)
+         jit_flags |= FLAG_OFFSET32;
+      if (jit_flags) jit_policy = std::max<int>(jit_policy, static_cast<int>(g_opt.jit));
+   }
    bool jit_used = false;
    auto launch_main = [&](const Params<T> &q, int g, int nv, int u_rt, int u_special, int w, long long grid, cudaStream_t s) -> bool {
+      const int fl = (g == G && nv == NV) ? jit_flags : (jit_flags & ~FLAG_EXACT_K);
       if (jit_policy > 0 && jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_special & 0xFF,
-                                              jit_budget(g, nv, u_special & 0xFF, u_special >> 8), w, q, grid, s, jit_policy,
+                                              jit_budget(g, nv, u_special & 0xFF, u_special >> 8), fl, w, q, grid, s, jit_policy,
                                               jit_weight)) {
          jit_used = true;
          return true;
       }
-      return launch_vec<T>(pattern, g, nv, u_rt, w, q, grid, s);
+      if (launch_vec<T>(pattern, g, nv, u_rt, w, q, grid, s)) return true;
+      // a tiling (option force_tiling / force_tiling_rows) that is not among the instantiations compiled into the
+      // library: build it at run time
+      if (g_opt.jit > 0 && g > 0 && 32 % g == 0 && nv > 0 && (u_rt & 0xFF) > 0 &&
+          jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_rt & 0xFF, u_rt >> 8, 0, w, q, grid, s, 2, jit_weight)) {
+         jit_used = true;
+         return true;
+      }
+      return false;
    };
 
    int launches = 0;
@@ -827,7 +867,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       launches += 2;
       if (with_rows) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
          q.mode = MODE_ROWS;
-         if (vec_ok) { if (!launch_main(q, Gr, NVr, Ur, g_opt.force_tiling_rows ? Ur : Us, warps, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
+         if (vec_ok) { if (!launch_main(q, Gr, NVr, Ur, Urs, warps, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
          else launch_any<T>(q, warps, qgrid, st);
          launches++;
       }
@@ -1396,7 +1436,7 @@ int fusedmm_b200_jit_prepare(int32_t dtype, int32_t imessage, int64_t k)
    int G = 0, NV = 0, U = 0;
    choose_tiling(k / W, dtype == 1, &G, &NV, &U);
    if (G == 0) return 0;
-   return jit_prepare(dtype, d.vop, d.rop, d.vsc, d.aop, G, NV, U & 0xFF, jit_budget(G, NV, U & 0xFF, U >> 8)) == 0 ? 0 : FUSEDMM_B200_ERR_NO_OPT;
+   return jit_prepare(dtype, d.vop, d.rop, d.vsc, d.aop, G, NV, U & 0xFF, jit_budget(G, NV, U & 0xFF, U >> 8), 0) == 0 ? 0 : FUSEDMM_B200_ERR_NO_OPT;
 }
 
 int fusedmm_b200_jit_stats(int64_t *out)
@@ -1495,6 +1535,7 @@ int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int6
    // split-row list, sized by its upper bound so that the scan cannot overflow it
    pl->chunk = std::max<int64_t>(32, g_opt.hub_chunk);
    if (ext > 0 && ext < (1ll << 24)) pl->chunk = std::min<long long>(pl->chunk, 128);  // as in a plain call; K is not known yet
+   if (ext > 0 && ext < (1ll << 21)) pl->chunk = std::min<long long>(pl->chunk, 64);
    const long long cap = ext / pl->chunk + 1;
    if (cudaMalloc(&pl->hub_row, cap * sizeof(long long)) != cudaSuccess || cudaMalloc(&pl->hub_base, cap * sizeof(long long)) != cudaSuccess ||
        cudaMalloc(&pl->counter, 256) != cudaSuccess) { cudaGetLastError(); return fail(FUSEDMM_B200_ERR_NOMEM); }
@@ -1669,6 +1710,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "multi_skip_empty_rows")) return &g_opt.multi_skip_empty_rows;
    if (!strcmp(name, "jit")) return &g_opt.jit;
    if (!strcmp(name, "pdl")) return &g_opt.pdl;
+   if (!strcmp(name, "jit_call_shape")) return &g_opt.jit_call_shape;
    if (!strcmp(name, "timing_detail")) return &g_opt.timing_detail;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
@@ -1707,7 +1749,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.engine || s == &g_opt.jit) && value > 2) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.engine || s == &g_opt.jit || s == &g_opt.jit_call_shape) && value > 2) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.chunk_ctas_per_sm && (value < 1 || value > 64)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.edge_quantum && (value < 32 || value > (1ll << 24))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.stream_depth && (value < 1 || value > 32)) return FUSEDMM_B200_ERR_ARG;

@@ -410,9 +410,19 @@ __device__ __forceinline__ void reduce_hub_row(const Params<T> &p, long long row
 // ---------------------------------------------------------------------------------------------------
 // Vector engine: one warp, one work item, K <= G*NV*W elements, everything 16-byte aligned.
 // ---------------------------------------------------------------------------------------------------
-template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U>
+// FLAGS: properties of the CALL (not of the message) that a kernel built at run time for that call may assume:
+//   FLAG_EXACT_K   k == G*NV*W: no vector of the tiling lies beyond the end of a row, so the per-vector bounds
+//                  predicates on every gather and store go away;
+//   FLAG_OFFSET32  column ids are 32 bits wide and every element offset into Y (cid*ldy + k) is below 2^32: the row
+//                  offset is one 32x32->64-bit multiply-add instead of a 64-bit multiply per edge.
+// The kernels compiled into the library use FLAGS = 0 and take every call.
+enum : int { FLAG_EXACT_K = 1, FLAG_OFFSET32 = 2 };
+
+template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U, int FLAGS = 0>
 struct VecEngine {
    static constexpr int W = VecOf<T>::W;
+   static constexpr bool EXACT_K = (FLAGS & FLAG_EXACT_K) != 0;
+   static constexpr bool OFFSET32 = (FLAGS & FLAG_OFFSET32) != 0;
    static constexpr int S = 32 / G;  // edge slots per warp
    // the flag-interpreting instantiation: stage codes are only known at run time
    static constexpr bool RUNTIME_CODES = VOPC < 0 || ROPC < 0 || VSCC < 0 || AOPC < 0;
@@ -443,7 +453,7 @@ struct VecEngine {
 #pragma unroll
       for (int v = 0; v < NV; v++) {
          const long long e0 = static_cast<long long>(v * G + lg) * W;
-         inb[v] = e0 < p.k;
+         inb[v] = EXACT_K || e0 < p.k;
 #pragma unroll
          for (int i = 0; i < W; i++) { xv[v][i] = T(0); acc[v][i] = aop_identity<T>(aop); }
          if (need_x && inb[v]) ld_vec(p.x + w.row * p.ldx + e0, xv[v]);
@@ -477,10 +487,16 @@ struct VecEngine {
             for (int u = 0; u < U; u++) {
                const int e = t + u * ES + eslot;  // < BW because ES*U divides BW
                ok[u] = e < nb;
-               const long long cid = p.idx64 ? (static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid >> 32), e, BW)) << 32) |
-                                                  static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW))
-                                             : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW));
-               const T *yrow = p.y + cid * p.ldy;
+               const T *yrow;
+               if constexpr (OFFSET32) {
+                  const unsigned int cid = static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW));
+                  yrow = p.y + static_cast<unsigned long long>(cid * static_cast<unsigned int>(p.ldy));
+               } else {
+                  const long long cid = p.idx64 ? (static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid >> 32), e, BW)) << 32) |
+                                                     static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW))
+                                                : static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW));
+                  yrow = p.y + cid * p.ldy;
+               }
 #pragma unroll
                for (int v = 0; v < NV; v++)
                   if (need_y && ok[u] && inb[v]) ld_vec_nc(yrow + static_cast<long long>(v * G + lg) * W, yv[u][v]);
@@ -569,12 +585,13 @@ constexpr int WARPS_PER_CTA = 8;  // upper bound; the launch chooses blockDim.x 
 // MB = resident 256-thread blocks per SM the register allocation must allow (0: the compiler's choice, 2: at most
 // 128 registers per thread, 3: 80, 4: 64): for some tilings a tighter budget (a few spills, more resident warps)
 // is faster.
-template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U, int MB>
+template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U, int MB, int FLAGS = 0>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32, MB)
 fused_vec_kernel(const Params<T> p)
 {
-   using Eng = VecEngine<T, VOPC, ROPC, VSCC, AOPC, G, NV, U>;
+   using Eng = VecEngine<T, VOPC, ROPC, VSCC, AOPC, G, NV, U, FLAGS>;
    constexpr int W = Eng::W;
+   constexpr bool EXACT_K = Eng::EXACT_K;
    const int lane = threadIdx.x & 31;
    const int aop = pick<AOPC>(p.aop);
    const int wpc = blockDim.x >> 5;
@@ -612,7 +629,7 @@ fused_vec_kernel(const Params<T> p)
 #pragma unroll
          for (int v = 0; v < NV; v++) {
             const long long e0 = static_cast<long long>(v * G + lg) * W;
-            if (e0 < p.k) {
+            if (EXACT_K || e0 < p.k) {
                if (p.accumulate) {
                   T old[W];
                   ld_vec(dst + e0, old);
@@ -655,7 +672,7 @@ fused_vec_kernel(const Params<T> p)
 #pragma unroll
          for (int v = 0; v < NV; v++) {
             const long long e0 = static_cast<long long>(v * G + lane) * W;
-            if (e0 < p.k) {
+            if (EXACT_K || e0 < p.k) {
                if (to_z && p.accumulate) {
                   T old[W];
                   ld_vec(dst + e0, old);
@@ -870,10 +887,10 @@ void launch_fixup(const Params<T> &p, long long grid, cudaStream_t stream);
 // found, compilation failed, the policy says this message is not worth compiling yet): the caller then launches the
 // flag-interpreting instantiation.  `weight` is the size of the call (edges x K, 0 if unknown) for that policy.
 template <typename T>
-bool jit_launch_vec(int vop, int rop, int vsc, int aop, int G, int NV, int U, int MB, int warps, const Params<T> &p,
+bool jit_launch_vec(int vop, int rop, int vsc, int aop, int G, int NV, int U, int MB, int flags, int warps, const Params<T> &p,
                     long long grid, cudaStream_t stream, int policy, long long weight);
 // Compile (or find in the cache) without launching; 0 on success.  Works without a GPU.
-int jit_prepare(int is_double, int vop, int rop, int vsc, int aop, int G, int NV, int U, int MB);
+int jit_prepare(int is_double, int vop, int rop, int vsc, int aop, int G, int NV, int U, int MB, int flags);
 struct JitStats { long long compiled, disk_hits, launches, failures; int nvrtc_found; };
 JitStats jit_stats();
 #endif

@@ -346,8 +346,8 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *   "accept_vop_noop" 0 (default): VOP_NOOP returns status 2 as in the reference (fusedMM.c:346-377);
  *                    1: VOP_NOOP means T = Y_v.
  *   "hub_chunk"      most edges a row may have before it is split across warps, and edges per piece
- *                    (default 256; a call whose nnz argument is below 2^24 uses at most 128 unless a row
- *                    of k values exceeds 1024 bytes).
+ *                    (default 256; a call whose nnz argument is below 2^24 uses at most 128, below 2^21
+ *                    at most 64, unless a row of k values exceeds 1024 bytes).
  *   "chunk_ctas_per_sm"  blocks per SM of the launch that works on the pieces of split rows (default 3).
  *   "force_tiling"   0 = automatic; otherwise (register_budget << 24) | (gathers_in_flight << 16) |
  *                    (lanes_per_edge << 8) | vectors_per_lane; gathers_in_flight 0 means that tiling's

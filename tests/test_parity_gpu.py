@@ -454,6 +454,47 @@ def test_run_time_built_kernels_for_messages_without_a_built_in_one(cuda_device,
     assert st == 0 and api.call_info().jit_kernel == 1 and api.jit_stats()["compiled"] == after["compiled"] + 1
 
 
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_kernels_built_for_the_shape_of_a_call(cuda_device, oracle, tmp_path, monkeypatch, vt):
+    """Option jit_call_shape = 2: every call whose K fills its tiling exactly, or whose Y lies within 2^32 elements
+    behind 32-bit column ids, runs a kernel built at run time for that shape (no bounds predicates, 32-bit row
+    offsets).  The four optimised messages and a generic one, K exact and ragged, int32 and int64 column ids,
+    against the oracle; results must also equal the built-in kernels' bit for bit (same arithmetic, same order)."""
+    monkeypatch.setenv("FUSEDMM_B200_JIT_CACHE", str(tmp_path / "jit"))
+    rng = np.random.default_rng(321)
+    m, n = 1500, 1300
+    w = 4 if vt == np.float32 else 2
+    seen = 0
+    try:
+        for k, it in ((32 * w, np.int32), (64 * w, np.int32), (64 * w - w, np.int32), (16 * w, np.int64), (8 * w, np.int32)):
+            pntrb, pntre, indx, val = random_csr(rng, m, n, 9, np.int64, it, hub=1700)
+            val = val.astype(vt)
+            x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+            for name in ("sigmoid", "tdist", "spmm", "gcn", "max_dot_copy_mul_min"):
+                msg, sop = MESSAGES[name], sop_for(name)
+                generic = name == "max_dot_copy_mul_min"
+                z0 = rng.uniform(-1, 1, size=(m, k)).astype(vt) if generic else np.zeros((m, k), vt)
+                want = z0.copy()
+                assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop,
+                                  zero_first=not generic) == 0
+                api.set_option("jit_call_shape", 0)
+                api.set_option("jit", 2)
+                st0, z_plain = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0.copy(), k, sop=sop)
+                api.set_option("jit_call_shape", 2)
+                st1, z_shape = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, z0.copy(), k, sop=sop)
+                info = api.call_info()
+                expect_jit = generic or it == np.int32 or k == info.lanes_per_edge * info.vectors_per_lane * w
+                assert st0 == st1 == 0 and info.jit_kernel == int(expect_jit), (name, k, it)
+                seen += info.jit_kernel
+                assert np.array_equal(z_plain, z_shape), (name, k, it)
+                tol = RTOL[np.dtype(vt)]
+                assert rel_err(z_shape, want) <= tol or generic, (name, k, it)
+    finally:
+        api.set_option("jit_call_shape", 0)
+        api.set_option("jit", 1)
+    assert seen >= 20
+
+
 def test_async_stream_entry(cuda_device, oracle):
     import torch
     rng = np.random.default_rng(10)
