@@ -11,7 +11,7 @@ namespace fmm {
 #define FMM_FOR_EACH_TILING(X) \
    X(4, 1, 4, 0) X(8, 1, 8, 0) X(8, 2, 4, 0) X(8, 4, 2, 0) X(16, 1, 8, 0) X(16, 2, 4, 0) X(16, 4, 2, 0) \
    X(32, 1, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 0) X(32, 8, 1, 0) \
-   X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3) X(16, 2, 4, 3)
+   X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3) X(16, 2, 4, 3) X(32, 2, 4, 3)
 
 // A translation unit may add tilings of its own by defining this before the include (the flag-interpreting
 // kernels need other register budgets than the specialised ones).

@@ -393,6 +393,12 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    a function that differs from the built-in only between or beyond the sample points is not
  *                    told apart.  1: such a hook is not examined and the call returns status 64; SOP_UDEF then
  *                    needs fusedmm_b200_set_sop or an explicit sop argument.
+ *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time for
+ *                    the shape of the call (exactly this K: no bounds predicates; 32-bit row offsets when column ids
+ *                    are 32 bits wide and Y lies within 2^32 elements); 2: every call does.  Bit-identical results;
+ *                    measured slower than the built-in kernels on three of four benchmark configurations.
+ *   "hub_cap_initial"  split rows the hub list has room for when it is first allocated (default 65536; it grows on
+ *                    demand, this only sets where the growth starts: tests use it to reach the growth path).
  *   "inject_alloc_failure"  n > 0: the n-th device allocation the library attempts from now on fails
  *                    with FUSEDMM_B200_ERR_NOMEM (host-side fault injection for tests; nothing is
  *                    done to the GPU).

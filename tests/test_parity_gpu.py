@@ -352,6 +352,38 @@ def test_scratch_grows_when_there_are_many_split_rows(cuda_device, oracle):
     assert rel_err(z, want) <= 1e-4
 
 
+def test_scratch_growth_in_the_blocked_copy_back_does_not_accumulate_twice(cuda_device, oracle):
+    """A host Z of 32 MB or more is computed and copied back in 8 blocks of rows.  With nnz = 0 (the reference never
+    reads nnz) nothing sizes the split-row scratch beforehand; when a block then finds it too small, only that
+    block's split rows are redone.  With beta = 1 every contribution must still be added exactly once."""
+    rng = np.random.default_rng(97)
+    m, n, k = 70_000, 5_000, 128          # Z: 35.8 MB
+    deg = rng.poisson(4, size=m)
+    hubs = rng.choice(m, size=2400, replace=False)
+    deg[hubs] = rng.integers(300, 700, size=hubs.size)   # 300 split rows per block of rows
+    rowptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    nnz = int(rowptr[-1])
+    indx = rng.integers(0, n, size=nnz).astype(np.int32)
+    val = rng.uniform(0.25, 1.5, size=nnz).astype(np.float32)
+    y = rng.uniform(-0.5, 0.5, size=(n, k)).astype(np.float32)
+    z0 = rng.uniform(-1, 1, size=(m, k)).astype(np.float32)
+    want = z0.copy()
+    assert oracle.csr(M.MSG_SPMM, m, n, k, val, indx, rowptr[:-1].copy(), rowptr[1:].copy(), y, k, y, k, 1.0, want, k,
+                      zero_first=False) == 0
+    api.lib().fusedmm_b200_release()
+    api.set_option("hub_cap_initial", 64)
+    try:
+        z = z0.copy()
+        st = api.fusedMM_csr(M.MSG_SPMM, m, n, k, 1.0, 0, m, n, val, indx, rowptr[:-1], rowptr[1:], None, k, y, k, 1.0, z, k)
+        info = api.call_info()
+    finally:
+        api.set_option("hub_cap_initial", 1 << 16)
+        api.lib().fusedmm_b200_release()
+    assert st == 0 and info.hub_rows == hubs.size
+    assert info.kernel_launches > 8 * 4          # 8 blocks, and the split rows of the blocks that overflowed again
+    assert rel_err(z, want) <= 1e-4
+
+
 def test_peer_stores_replicate_finished_rows(cuda_device, oracle):
     """fusedmm_b200_csr_multi: finished rows also go to the peers' Z buffers.  Two more buffers on the same
     GPU stand in for the peers (on several GPUs the addresses come from peer-mapped memory); vector engine
