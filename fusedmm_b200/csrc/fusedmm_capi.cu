@@ -12,6 +12,7 @@
 #include <nvtx3/nvToolsExt.h>  // header-only: the ranges cost nothing unless a profiler is attached
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -96,7 +97,7 @@ bool launch_stream<double>(int pattern, int G, int NV, int warps, const Params<d
 template <typename T>
 void launch_any(const Params<T> &p, int warps, long long grid, cudaStream_t s)
 {
-   launch_kernel<T>(fused_any_kernel<T>, grid, warps * 32, s, p);
+   launch_kernel<T>(fused_any_kernel<T>, grid, warps * 32, s, p, static_cast<size_t>(warps) * ANY_MAX_CACHED * sizeof(T));
 }
 template <typename T>
 void launch_fixup(const Params<T> &p, long long grid, cudaStream_t s)
@@ -161,6 +162,7 @@ struct DevBuf {
 };
 
 struct DeviceCtx {
+   std::mutex mu;  // one call at a time per device; calls on different devices (from different host threads) overlap
    int device = -1;
    bool ready = false;
    cudaStream_t stream = nullptr;
@@ -191,12 +193,17 @@ struct DeviceCtx {
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, hub_cap_initial = 1 << 16;
+           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, exact_k = 1, hub_cap_initial = 1 << 16;
 };
 
+// Locking: g_mu guards the process-wide settings (options, default SOP) and the creation of device contexts; each
+// device context has its own mutex for the body of a call.  A call copies the options into t_opt under g_mu and works
+// on that copy, so host threads that drive different GPUs run their calls side by side.
+constexpr int MAX_DEVICES = 64;
 std::mutex g_mu;
-std::vector<DeviceCtx> g_ctx;
+DeviceCtx g_ctx[MAX_DEVICES];
 Options g_opt;
+thread_local Options t_opt;
 fusedmm_b200_sop g_sop = {FUSEDMM_SOP_SIGMOID, 0, 0.0, 0.0, 0.0};
 thread_local fusedmm_b200_call_info t_info = {};
 
@@ -241,11 +248,12 @@ int ensure_buf(DevBuf &b, size_t bytes)
    return 0;
 }
 
+// Caller holds g_mu.
 int get_ctx(DeviceCtx **out)
 {
    int dev = 0;
    CK(cudaGetDevice(&dev));
-   if (static_cast<int>(g_ctx.size()) <= dev) g_ctx.resize(dev + 1);
+   if (dev < 0 || dev >= MAX_DEVICES) return FUSEDMM_B200_ERR_LIMIT;
    DeviceCtx &c = g_ctx[dev];
    if (!c.ready) {
       c.device = dev;
@@ -269,6 +277,19 @@ int get_ctx(DeviceCtx **out)
       c.ready = true;
    }
    *out = &c;
+   return 0;
+}
+
+// Snapshot of the settings + the current device's context, then that device's lock (held until `lk` dies).
+int enter_device(DeviceCtx **c, std::unique_lock<std::mutex> *lk, fusedmm_b200_sop *default_sop = nullptr)
+{
+   {
+      std::lock_guard<std::mutex> lock(g_mu);
+      t_opt = g_opt;
+      if (default_sop) *default_sop = g_sop;
+      CKI(get_ctx(c));
+   }
+   *lk = std::unique_lock<std::mutex>((*c)->mu);
    return 0;
 }
 
@@ -438,6 +459,7 @@ void choose_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
    else if (nvec <= 64) { *G = 32; *NV = 2; *U = is_double ? 8 : 4; }
    else if (nvec <= 128) { *G = 32; *NV = 4; *U = 2 | (3 << 8); }
    else if (nvec <= 256) { *G = 32; *NV = 8; *U = 1; }
+   else if (nvec <= 512) { *G = 32; *NV = 16; *U = 1; }  // 2048 floats / 1024 doubles: X_u, Z_u and one gathered row = 192 registers
    else { *G = 0; *NV = 0; *U = 0; }
 }
 // The whole-row launch may use other gathers in flight / register budget than the chunk launch: its rows are short
@@ -462,9 +484,10 @@ void tiling_for_generic(int G, int NV, int *U)
    else if (G == 32 && NV == 2 && *U == 4) *U = 4 | (3 << 8);
    else if (G == 16 && NV == 2 && *U == 8) *U = 4;
 }
-// Register budget of a kernel built at run time.  For three tilings the offline compiler settles on 80 registers
-// (with a few spilled values) without being asked to, and the tilings were tuned with that; NVRTC gives the same
-// source 96-106 registers, one resident block fewer per SM.  Ask for the 80-register budget explicitly there.
+// Register budget of a kernel built at run time (and of the exact-K instantiations).  For three tilings the offline
+// compiler settles on 80 registers (with a few spilled values) without being asked to, and the tilings were tuned with
+// that; NVRTC gives the same source 96-106 registers, one resident block fewer per SM, and so does the offline compiler
+// once the bounds predicates are gone.  Ask for the 80-register budget explicitly there.
 int jit_budget(int G, int NV, int U, int MB)
 {
    if (MB == 0 && ((G == 32 && NV == 2 && U == 4) || (G == 32 && NV == 1 && U == 8) || (G == 16 && NV == 1 && U == 8))) return 3;
@@ -522,7 +545,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
 
    // accumulate?  (beta semantics: see "beta_mode" in fusedmm_b200.h)
    const bool opt_pattern = d.pattern != PAT_GENERIC;
-   const int accumulate = (g_opt.beta_mode == 0 && opt_pattern) ? (a.beta != 0.0) : 1;
+   const int accumulate = (t_opt.beta_mode == 0 && opt_pattern) ? (a.beta != 0.0) : 1;
 
    // ---- residency and staging ----------------------------------------------------------------------
    std::unique_ptr<NvtxRange> stage_range(new NvtxRange("fusedmm_b200: residency + staging"));
@@ -635,7 +658,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    p.sop_kind = sopk.kind;
    p.sp0 = static_cast<T>(sopk.p0); p.sp1 = static_cast<T>(sopk.p1); p.sp2 = static_cast<T>(sopk.p2);
    p.accumulate = accumulate;
-   p.chunk = std::max<int64_t>(32, g_opt.hub_chunk);
+   p.chunk = std::max<int64_t>(32, t_opt.hub_chunk);
    // Shorter pieces for small graphs (more work items, shorter critical path): measured on R-MAT graphs of
    // 2-260 M edges, 128 wins below about 16 M edges unless rows are long in bytes, 256 is within 1 % of the
    // best everywhere else.  nnz is only a hint here (the reference never reads it); a wrong value costs
@@ -660,7 +683,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          p.z_peer[i] = static_cast<T *>(a.z_peers[i]);
       }
    }
-   p.skip_empty_remote = (p.z_mc || p.n_peers > 0) && g_opt.multi_skip_empty_rows;
+   p.skip_empty_remote = (p.z_mc || p.n_peers > 0) && t_opt.multi_skip_empty_rows;
    if (d.sop == OP_UDEF && sopk.kind == FUSEDMM_SOP_SIGMOID_TABLE_C) {
       DevBuf &tb = sizeof(T) == 4 ? c.table_f : c.table_d;
       if (!tb.ptr) {
@@ -681,69 +704,80 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    if (p.z_mc) vec_ok = vec_ok && aligned16(p.z_mc);
    int G = 0, NV = 0, U = 0;
    int Us = 0;  // gathers in flight and register budget of a kernel specialised for the message (U is the flag-interpreting kernel's)
-   const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
+   const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(t_opt.warps_per_cta, 1), WARPS_PER_CTA));
    if (vec_ok) {
-      if (g_opt.force_tiling) {
-         G = static_cast<int>((g_opt.force_tiling >> 8) & 0xFF);
-         NV = static_cast<int>(g_opt.force_tiling & 0xFF);
-         U = static_cast<int>((g_opt.force_tiling >> 16) & 0xFF);
+      if (t_opt.force_tiling) {
+         G = static_cast<int>((t_opt.force_tiling >> 8) & 0xFF);
+         NV = static_cast<int>(t_opt.force_tiling & 0xFF);
+         U = static_cast<int>((t_opt.force_tiling >> 16) & 0xFF);
          if (U == 0) U = default_u(G, NV);
-         U |= static_cast<int>((g_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
+         U |= static_cast<int>((t_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
       } else {
          choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
          Us = U;
-         if (g_opt.force_generic || d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
+         if (t_opt.force_generic || d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
       }
       if (Us == 0) Us = U;
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
    int Gr = G, NVr = NV, Ur = U, Urs = Us;  // Urs: U | budget of a specialised kernel for the whole rows
-   if (vec_ok && !g_opt.force_tiling && !g_opt.force_tiling_rows) {
+   if (vec_ok && !t_opt.force_tiling && !t_opt.force_tiling_rows) {
       int g2 = 0, nv2 = 0, u2 = 0;
       if (choose_rows_tiling(a.k / W, sizeof(T) == 8, &g2, &nv2, &u2) && static_cast<long long>(g2) * nv2 * W >= a.k) {
-         if (d.pattern != PAT_GENERIC && !g_opt.force_generic) { Gr = g2; NVr = nv2; Ur = u2; Urs = u2; }
+         if (d.pattern != PAT_GENERIC && !t_opt.force_generic) { Gr = g2; NVr = nv2; Ur = u2; Urs = u2; }
          else if (g2 == G && nv2 == NV) Urs = u2;  // the flag-interpreting kernel keeps its own; one built for the message takes it
       }
    }
-   if (vec_ok && g_opt.force_tiling_rows) {
-      Gr = static_cast<int>((g_opt.force_tiling_rows >> 8) & 0xFF);
-      NVr = static_cast<int>(g_opt.force_tiling_rows & 0xFF);
-      Ur = static_cast<int>((g_opt.force_tiling_rows >> 16) & 0xFF);
+   if (vec_ok && t_opt.force_tiling_rows) {
+      Gr = static_cast<int>((t_opt.force_tiling_rows >> 8) & 0xFF);
+      NVr = static_cast<int>(t_opt.force_tiling_rows & 0xFF);
+      Ur = static_cast<int>((t_opt.force_tiling_rows >> 16) & 0xFF);
       if (Ur == 0) Ur = default_u(Gr, NVr);
-      Ur |= static_cast<int>((g_opt.force_tiling_rows >> 24) & 0xFF) << 8;
+      Ur |= static_cast<int>((t_opt.force_tiling_rows >> 24) & 0xFF) << 8;
       Urs = Ur;
       if (Gr == 0 || 32 % Gr != 0 || static_cast<long long>(Gr) * NVr * W < a.k) return FUSEDMM_B200_ERR_ARG;
    }
-   const int pattern = g_opt.force_generic ? PAT_GENERIC : d.pattern;
+   const int pattern = t_opt.force_generic ? PAT_GENERIC : d.pattern;
    // A message without a built-in specialised kernel gets one built at run time (fusedmm_jit.cu) when the policy of
    // option "jit" says it is worth it; otherwise, or when that fails, the flag-interpreting instantiation runs.
    const long long jit_weight = a.nnz > 0 && a.nnz < (1ll << 40) ? a.nnz * a.k : 0;
-   int jit_policy = ((d.pattern == PAT_GENERIC && !g_opt.force_generic) || g_opt.force_generic == 2) ? static_cast<int>(g_opt.jit) : 0;
+   int jit_policy = ((d.pattern == PAT_GENERIC && !t_opt.force_generic) || t_opt.force_generic == 2) ? static_cast<int>(t_opt.jit) : 0;
    // Option "jit_call_shape": a large call of ANY message (the four patterns included) gets a kernel built for the
    // shape of the call too: exactly this K (no bounds predicates on the vectors of a row) and, when column ids are
    // 32 bits wide and all of Y lies within 2^32 elements, 32-bit row offsets.
+   // A call whose K fills its tiling exactly runs the instantiation without per-vector bounds predicates
+   // (FLAG_EXACT_K; compiled in for the default tilings, built at run time for messages outside the four patterns).
+   // 32-bit row offsets (FLAG_OFFSET32) exist only as an experiment behind option "jit_call_shape".
    int jit_flags = 0;
-   if (vec_ok && g_opt.jit_call_shape && g_opt.jit > 0 && !g_opt.force_generic && (jit_weight >= (1ll << 26) || g_opt.jit_call_shape == 2)) {
-      if (static_cast<long long>(G) * NV * W == a.k) jit_flags |= FLAG_EXACT_K;
+   if (vec_ok && t_opt.jit_call_shape && t_opt.jit > 0 && !t_opt.force_generic && (jit_weight >= (1ll << 26) || t_opt.jit_call_shape == 2)) {
       const bool need_y_ = vop_reads_y(d.vop);
       if (need_y_ && a.idx_bits == 32 && a.n > 0 && static_cast<double>(a.n - 1) * static_cast<double>(a.ldy) + static_cast<double>(a.k) <= 4294967295.0)
          jit_flags |= FLAG_OFFSET32;
-      if (jit_flags) jit_policy = std::max<int>(jit_policy, static_cast<int>(g_opt.jit));
+      jit_flags &= static_cast<int>(t_opt.jit_shape_mask);
+      if (jit_flags & FLAG_OFFSET32) jit_policy = std::max<int>(jit_policy, static_cast<int>(t_opt.jit));
    }
    bool jit_used = false;
    auto launch_main = [&](const Params<T> &q, int g, int nv, int u_rt, int u_special, int w, long long grid, cudaStream_t s) -> bool {
-      const int fl = (g == G && nv == NV) ? jit_flags : (jit_flags & ~FLAG_EXACT_K);
+      const bool ex = t_opt.exact_k && static_cast<long long>(g) * nv * W == a.k;  // per launch: the whole rows may have their own tiling
+      const int fl = (jit_flags & ~FLAG_EXACT_K) | (ex ? FLAG_EXACT_K : 0);
       if (jit_policy > 0 && jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_special & 0xFF,
                                               jit_budget(g, nv, u_special & 0xFF, u_special >> 8), fl, w, q, grid, s, jit_policy,
                                               jit_weight)) {
          jit_used = true;
          return true;
       }
+      if (fl & FLAG_EXACT_K) {
+         // without the predicates the offline compiler no longer settles on 80 registers for (32, 2, 4) by itself (93):
+         // ask for the budget the tiling was tuned with
+         const int u_budget = (u_rt & 0xFF) | (jit_budget(g, nv, u_rt & 0xFF, (u_rt >> 8) & 0xFF) << 8);
+         if (launch_vec<T>(pattern, g, nv, u_budget | (1 << 16), w, q, grid, s)) return true;
+         if (launch_vec<T>(pattern, g, nv, u_rt | (1 << 16), w, q, grid, s)) return true;
+      }
       if (launch_vec<T>(pattern, g, nv, u_rt, w, q, grid, s)) return true;
       // a tiling (option force_tiling / force_tiling_rows) that is not among the instantiations compiled into the
       // library: build it at run time
-      if (g_opt.jit > 0 && g > 0 && 32 % g == 0 && nv > 0 && (u_rt & 0xFF) > 0 &&
+      if (t_opt.jit > 0 && g > 0 && 32 % g == 0 && nv > 0 && (u_rt & 0xFF) > 0 &&
           jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_rt & 0xFF, u_rt >> 8, 0, w, q, grid, s, 2, jit_weight)) {
          jit_used = true;
          return true;
@@ -758,14 +792,14 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // The edge-stream scheduler needs row r+1 to start where row r ends, which the usual
    // (rowptr, rowptr+1) way of passing pntrb/pntre guarantees; anything else takes the row scheduler.
    const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
-   const bool use_stream = vec_ok && contiguous_rows && g_opt.engine == 2 && p.n_peers == 0 && !p.z_mc && !a.plan;
+   const bool use_stream = vec_ok && contiguous_rows && t_opt.engine == 2 && p.n_peers == 0 && !p.z_mc && !a.plan && NV <= 8;
    p.counter = static_cast<unsigned long long *>(c.counter.ptr);
 
    if (use_stream) {
       // ---- edge-stream scheduler: partition, main kernel, fix-up ------------------------------------
-      p.quantum = (g_opt.edge_quantum + 31) / 32 * 32;
+      p.quantum = (t_opt.edge_quantum + 31) / 32 * 32;
       int depth = std::min(G, 8);  // at least one segment; a power of two <= 32
-      while (depth * 2 <= std::min<int64_t>(g_opt.stream_depth, 32)) depth *= 2;
+      while (depth * 2 <= std::min<int64_t>(t_opt.stream_depth, 32)) depth *= 2;
       p.depth = depth;
       if (c.part_cap == 0 || c.heads.bytes == 0) {
          long long want = 1 << 16;
@@ -818,7 +852,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    } else {
    // ---- row scheduler: whole rows, chunks of long rows, fix-up ----------------------------------------
    if (c.hub_cap == 0) {
-      c.hub_cap = std::max<int64_t>(16, g_opt.hub_cap_initial);
+      c.hub_cap = std::max<int64_t>(16, t_opt.hub_cap_initial);
       CKI(ensure_buf(c.hub_row, c.hub_cap * sizeof(long long)));
       CKI(ensure_buf(c.hub_base, c.hub_cap * sizeof(long long)));
    }
@@ -843,7 +877,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       }
    }
    const long long rows_per_warp = vec_ok ? 32 / Gr : 1;  // short rows: one per group of lanes
-   const long long hub_grid = static_cast<long long>(c.sm_count) * g_opt.chunk_ctas_per_sm;
+   const long long hub_grid = static_cast<long long>(c.sm_count) * t_opt.chunk_ctas_per_sm;
 
    // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
    // (and their fix-up) on the side stream beside the whole rows on `st`, forked after the scan and joined
@@ -856,9 +890,9 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       // predecessor drains (programmatic dependent launch).
       if (timing) CK(cudaEventRecord(c.evk[0], st));
       CK(cudaEventRecord(c.ev_fork, st));
-      cudaStream_t side = !g_opt.side_stream ? st : (g_opt.side_priority ? c.side_hi : c.side);
+      cudaStream_t side = !t_opt.side_stream ? st : (t_opt.side_priority ? c.side_hi : c.side);
       CK(cudaStreamWaitEvent(side, c.ev_fork, 0));
-      const bool pdl = g_opt.pdl != 0;
+      const bool pdl = t_opt.pdl != 0;
       if (!a.plan) {  // a plan carries the result of this scan
          CK(cudaMemsetAsync(q.counter, 0, sizeof(unsigned long long), side));
          scan_hub_rows<<<static_cast<unsigned int>((q.m + 255) / 256), 256, 0, side>>>(
@@ -866,7 +900,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          launches++;
       }
       // events between the kernels of the chain (option timing_detail) would undo the pairing of the launches
-      const bool detail = timing && g_opt.timing_detail;
+      const bool detail = timing && t_opt.timing_detail;
       if (detail) CK(cudaEventRecord(c.evk[2], side));
       q.mode = MODE_HUB_CHUNKS;
       q.pdl = pdl && !a.plan && !detail;
@@ -985,7 +1019,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       float t = 0.f;
       CK(cudaEventElapsedTime(&t, c.ev0, c.ev1));
       ms += t;
-      if (g_opt.timing_detail) {
+      if (t_opt.timing_detail) {
          CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[2])); ms_k[0] += t;   // start of the pass -> scan done
          CK(cudaEventElapsedTime(&t, c.evk[0], c.evk[1])); ms_k[1] += t;   // whole rows, beside the chain
          CK(cudaEventElapsedTime(&t, c.evk[2], c.evk[3])); ms_k[2] += t;
@@ -1044,20 +1078,24 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
              void *z_multicast = nullptr, const fusedmm_b200_plan *plan = nullptr)
 {
    NvtxRange call_range("fusedmm_b200: fusedMM_csr");
-   std::lock_guard<std::mutex> lock(g_mu);
    memset(&t_info, 0, sizeof(t_info));
    if ((dtype != 0 && dtype != 1) || (ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64))
       return FUSEDMM_B200_ERR_ARG;
+   fusedmm_b200_sop sopk;
+   {
+      std::lock_guard<std::mutex> lock(g_mu);
+      t_opt = g_opt;
+      sopk = g_sop;
+   }
    Decoded d;
-   int st = decode_message(imessage, g_opt, &d);
+   int st = decode_message(imessage, t_opt, &d);
    if (st) return st;
-   fusedmm_b200_sop sopk = g_sop;
    if (d.sop == OP_UDEF) {
       if (sop) {
          if (sop->kind < 0 || sop->kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_UDEF;
          sopk = *sop;
       } else if (hook) {
-         if (g_opt.strict_udef) {
+         if (t_opt.strict_udef) {
             fprintf(stderr, "fusedmm_b200: option strict_udef is set: SOP_UDEF needs an explicit scalar function "
                             "(fusedmm_b200_set_sop or the sop argument), a host SOP_UDEF_FUNC is not examined\n");
             return FUSEDMM_B200_ERR_UDEF;
@@ -1069,19 +1107,17 @@ int run_call(int32_t dtype, int32_t ptr_bits, int32_t idx_bits, int32_t imessage
                             "(see FUSEDMM_SOP_* in fusedmm_b200.h)\n");
             return FUSEDMM_B200_ERR_UDEF;
          }
-         static bool told = false;  // once per process: which device function stands in for the caller's host function
-         if (!told && getenv("FUSEDMM_B200_TRACE")) {
-            told = true;
+         static std::atomic<bool> told{false};  // once per process: which device function stands in for the caller's host function
+         if (getenv("FUSEDMM_B200_TRACE") && !told.exchange(true))
             fprintf(stderr, "fusedmm_b200: SOP_UDEF_FUNC matches built-in scalar function %d at the sample points "
                             "(FUSEDMM_SOP_* in fusedmm_b200.h); the device evaluates that function\n", sopk.kind);
-         }
       }
    }
    if (m < 0 || k < 0) return FUSEDMM_B200_ERR_ARG;
    if (d.aop == AOP_NOOP || m == 0 || k == 0) return 0;  // nothing is written to Z (fusedMM.c:268-273)
    DeviceCtx *c = nullptr;
-   st = get_ctx(&c);
-   if (st) return st;
+   std::unique_lock<std::mutex> device_lock;
+   CKI(enter_device(&c, &device_lock));
    HostArgs a = {imessage, m, n, k, nnz, val, indx, pntrb, pntre, x, y, z, ldx, ldy, ldz, beta, ptr_bits, idx_bits, n_peers, z_peers, z_multicast, plan};
    return dtype == 0 ? run_typed<float>(*c, a, d, sopk, static_cast<cudaStream_t>(stream))
                      : run_typed<double>(*c, a, d, sopk, static_cast<cudaStream_t>(stream));
@@ -1107,6 +1143,7 @@ constexpr size_t STATIC_OFF_TABLE_D = STATIC_OFF_TABLE_F + SM_TABLE_SIZE * sizeo
 constexpr size_t STATIC_OFF_HUB_ROW = STATIC_OFF_TABLE_D + SM_TABLE_SIZE * sizeof(double);
 constexpr size_t STATIC_OFF_HUB_BASE = STATIC_OFF_HUB_ROW + STATIC_HUB_CAP * sizeof(long long);
 constexpr size_t STATIC_OFF_PARTIALS = STATIC_OFF_HUB_BASE + STATIC_HUB_CAP * sizeof(long long);
+static_assert(STATIC_MAX_DEVICES == MAX_DEVICES, "one slot per device context");
 static_assert(STATIC_OFF_PARTIALS % 256 == 0, "the partial sums must start on a 256-byte boundary");
 
 struct StaticScratchSlot {
@@ -1195,8 +1232,8 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
    p.vop = d.vop; p.rop = d.rop; p.sop = d.sop; p.vsc = d.vsc; p.aop = d.aop;
    p.sop_kind = sopk.kind;
    p.sp0 = static_cast<T>(sopk.p0); p.sp1 = static_cast<T>(sopk.p1); p.sp2 = static_cast<T>(sopk.p2);
-   p.accumulate = (g_opt.beta_mode == 0 && d.pattern != PAT_GENERIC) ? (a.beta != 0.0) : 1;
-   p.chunk = std::max<int64_t>(512, g_opt.hub_chunk);  // fixed scratch: fewer, longer pieces than the default
+   p.accumulate = (t_opt.beta_mode == 0 && d.pattern != PAT_GENERIC) ? (a.beta != 0.0) : 1;
+   p.chunk = std::max<int64_t>(512, t_opt.hub_chunk);  // fixed scratch: fewer, longer pieces than the default
    p.counter = reinterpret_cast<unsigned long long *>(slot->base);
    p.hub_row = reinterpret_cast<long long *>(slot->base + STATIC_OFF_HUB_ROW);
    p.hub_base = reinterpret_cast<long long *>(slot->base + STATIC_OFF_HUB_BASE);
@@ -1228,7 +1265,7 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
       if (d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
       if (G == 0) vec_ok = false;
    }
-   const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(g_opt.warps_per_cta, 1), WARPS_PER_CTA));
+   const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(t_opt.warps_per_cta, 1), WARPS_PER_CTA));
    const long long rows_per_warp = vec_ok ? 32 / G : 1;
    const long long row_grid = (a.m + warps * rows_per_warp - 1) / (warps * rows_per_warp);
    const long long hub_grid = static_cast<long long>(slot->sm_count) * 8;
@@ -1238,12 +1275,14 @@ int run_static_scratch(const HostArgs &a, const Decoded &d, const fusedmm_b200_s
    CK(cudaMemsetAsync(p.counter, 0, sizeof(unsigned long long), st));
    scan_hub_rows<<<static_cast<unsigned int>((a.m + 255) / 256), 256, 0, st>>>(
       p.pntrb, p.pntre, p.ptr64, p.m, p.chunk, p.counter, p.hub_row, p.hub_base, p.hub_cap);
+   // K fills the tiling exactly: the instantiation without bounds predicates, where it is compiled in
+   const int Ux = (t_opt.exact_k && static_cast<long long>(G) * NV * W == a.k) ? (U | (1 << 16)) : U;
    p.mode = MODE_HUB_CHUNKS;
-   if (vec_ok) { if (!launch_vec<T>(d.pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, st)) return FUSEDMM_B200_ERR_ARG; }
+   if (vec_ok) { if (!launch_vec<T>(d.pattern, G, NV, Ux, WARPS_PER_CTA, p, hub_grid, st) && !launch_vec<T>(d.pattern, G, NV, U, WARPS_PER_CTA, p, hub_grid, st)) return FUSEDMM_B200_ERR_ARG; }
    else launch_any<T>(p, WARPS_PER_CTA, hub_grid, st);
    launch_fixup<T>(p, slot->sm_count, st);
    p.mode = MODE_ROWS;
-   if (vec_ok) { if (!launch_vec<T>(d.pattern, G, NV, U, warps, p, row_grid, st)) return FUSEDMM_B200_ERR_ARG; }
+   if (vec_ok) { if (!launch_vec<T>(d.pattern, G, NV, Ux, warps, p, row_grid, st) && !launch_vec<T>(d.pattern, G, NV, U, warps, p, row_grid, st)) return FUSEDMM_B200_ERR_ARG; }
    else launch_any<T>(p, warps, row_grid, st);
    CK(cudaGetLastError());
    long long nh = 0, nchunks = 0;
@@ -1441,10 +1480,13 @@ int fusedmm_b200_zero_empty_rows(int32_t dtype, int32_t ptr_bits, int64_t m, int
 
 int fusedmm_b200_jit_prepare(int32_t dtype, int32_t imessage, int64_t k)
 {
-   std::lock_guard<std::mutex> lock(g_mu);
+   {
+      std::lock_guard<std::mutex> lock(g_mu);
+      t_opt = g_opt;
+   }
    if ((dtype != 0 && dtype != 1) || k <= 0) return FUSEDMM_B200_ERR_ARG;
    Decoded d;
-   int st = decode_message(imessage, g_opt, &d);
+   int st = decode_message(imessage, t_opt, &d);
    if (st) return st;
    if (d.pattern != PAT_GENERIC || d.aop == AOP_NOOP) return 0;  // built in, or nothing to compute
    const int W = dtype == 0 ? 4 : 2;
@@ -1458,7 +1500,6 @@ int fusedmm_b200_jit_prepare(int32_t dtype, int32_t imessage, int64_t k)
 int fusedmm_b200_jit_stats(int64_t *out)
 {
    if (!out) return FUSEDMM_B200_ERR_ARG;
-   std::lock_guard<std::mutex> lock(g_mu);
    const JitStats s = jit_stats();
    out[0] = s.compiled; out[1] = s.disk_hits; out[2] = s.launches; out[3] = s.failures; out[4] = s.nvrtc_found;
    return 0;
@@ -1486,13 +1527,22 @@ int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx
                                     int64_t ldz, const fusedmm_b200_sop *sop, void *stream)
 {
    (void)alpha; (void)rows; (void)cols;
-   std::lock_guard<std::mutex> lock(g_mu);
    if ((dtype != 0 && dtype != 1) || (ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64))
       return FUSEDMM_B200_ERR_ARG;
+   fusedmm_b200_sop sopk;
+   {
+      std::lock_guard<std::mutex> lock(g_mu);
+      t_opt = g_opt;
+      sopk = g_sop;
+   }
+   // the array is per device: one call at a time per device (no context is created: that would allocate)
+   int dev = 0;
+   CK(cudaGetDevice(&dev));
+   if (dev < 0 || dev >= MAX_DEVICES) return FUSEDMM_B200_ERR_LIMIT;
+   std::lock_guard<std::mutex> device_lock(g_ctx[dev].mu);
    Decoded d;
-   int st = decode_message(imessage, g_opt, &d);
+   int st = decode_message(imessage, t_opt, &d);
    if (st) return st;
-   fusedmm_b200_sop sopk = g_sop;
    if (d.sop == OP_UDEF && sop) {
       if (sop->kind < 0 || sop->kind >= FUSEDMM_SOP_KIND_COUNT) return FUSEDMM_B200_ERR_UDEF;
       sopk = *sop;
@@ -1509,13 +1559,13 @@ int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int6
                              fusedmm_b200_plan **out)
 {
    (void)nnz;
-   std::lock_guard<std::mutex> lock(g_mu);
    if (!out || m < 0 || (ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64) ||
        (val && val_dtype != 0 && val_dtype != 1) || (m > 0 && (!pntrb || !pntre)))
       return FUSEDMM_B200_ERR_ARG;
    *out = nullptr;
    DeviceCtx *c = nullptr;
-   CKI(get_ctx(&c));
+   std::unique_lock<std::mutex> device_lock;
+   CKI(enter_device(&c, &device_lock));
    CK(cudaDeviceSynchronize());
    fusedmm_b200_plan *pl = new fusedmm_b200_plan();
    pl->device = c->device;
@@ -1549,7 +1599,7 @@ int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int6
       *dst[i] = pl->own[i];
    }
    // split-row list, sized by its upper bound so that the scan cannot overflow it
-   pl->chunk = std::max<int64_t>(32, g_opt.hub_chunk);
+   pl->chunk = std::max<int64_t>(32, t_opt.hub_chunk);
    if (ext > 0 && ext < (1ll << 24)) pl->chunk = std::min<long long>(pl->chunk, 128);  // as in a plain call; K is not known yet
    if (ext > 0 && ext < (1ll << 21)) pl->chunk = std::min<long long>(pl->chunk, 64);
    const long long cap = ext / pl->chunk + 1;
@@ -1596,12 +1646,12 @@ int fusedmm_b200_plan_destroy(fusedmm_b200_plan *plan)
 
 int fusedmm_b200_stream_status(void)
 {
-   std::lock_guard<std::mutex> lock(g_mu);
+   int cur_dev = -1;
+   if (cudaGetDevice(&cur_dev) != cudaSuccess || cur_dev < 0 || cur_dev >= MAX_DEVICES) { cudaGetLastError(); return FUSEDMM_B200_ERR_CUDA; }
+   std::unique_lock<std::mutex> device_lock(g_ctx[cur_dev].mu);
    {  // a call of the entry point that allocates nothing, enqueued on a caller's stream (nothing is allocated here either)
-      int dev = -1;
-      if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < STATIC_MAX_DEVICES && g_static_slot[dev].base &&
-          g_static_slot[dev].async_pending) {
-         StaticScratchSlot &slot = g_static_slot[dev];
+      if (g_static_slot[cur_dev].base && g_static_slot[cur_dev].async_pending) {
+         StaticScratchSlot &slot = g_static_slot[cur_dev];
          unsigned long long packed = 0;
          CK(cudaMemcpy(&packed, slot.base, sizeof(packed), cudaMemcpyDeviceToHost));
          slot.async_pending = false;
@@ -1610,10 +1660,8 @@ int fusedmm_b200_stream_status(void)
             return FUSEDMM_B200_ERR_LIMIT;  // nnz understated the graph: the split rows of that call were not computed
       }
    }
-   DeviceCtx *c = nullptr;
-   int st = get_ctx(&c);
-   if (st) return st;
-   if (!c->async_pending) return 0;
+   DeviceCtx *c = &g_ctx[cur_dev];
+   if (!c->ready || !c->async_pending) return 0;
    unsigned long long words[2] = {0, 0};
    CK(cudaMemcpy(words, c->counter.ptr, sizeof(words), cudaMemcpyDeviceToHost));
    c->async_pending = false;
@@ -1643,13 +1691,13 @@ int fusedmm_b200_stream_status(void)
 int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_t n, const void *indx,
                            const void *pntrb, const void *pntre, int64_t *report)
 {
-   std::lock_guard<std::mutex> lock(g_mu);
    if ((ptr_bits != 32 && ptr_bits != 64) || (idx_bits != 32 && idx_bits != 64) || m < 0 || !report) return FUSEDMM_B200_ERR_ARG;
    for (int i = 0; i < 4; i++) report[i] = 0;
    if (m == 0) return 0;
    if (!pntrb || !pntre || !indx) return FUSEDMM_B200_ERR_ARG;
    DeviceCtx *c = nullptr;
-   CKI(get_ctx(&c));
+   std::unique_lock<std::mutex> device_lock;
+   CKI(enter_device(&c, &device_lock));
    const size_t ps = ptr_bits / 8, is = idx_bits / 8;
    const void *dpb = pntrb, *dpe = pntre, *dix = indx;
    CK(cudaDeviceSynchronize());
@@ -1728,6 +1776,8 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "pdl")) return &g_opt.pdl;
    if (!strcmp(name, "jit_call_shape")) return &g_opt.jit_call_shape;
    if (!strcmp(name, "hub_cap_initial")) return &g_opt.hub_cap_initial;
+   if (!strcmp(name, "jit_shape_mask")) return &g_opt.jit_shape_mask;
+   if (!strcmp(name, "exact_k")) return &g_opt.exact_k;
    if (!strcmp(name, "timing_detail")) return &g_opt.timing_detail;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
@@ -1763,7 +1813,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    int64_t *s = option_slot(name);
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.force_generic && value > 2) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail || s == &g_opt.exact_k) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if ((s == &g_opt.engine || s == &g_opt.jit || s == &g_opt.jit_call_shape) && value > 2) return FUSEDMM_B200_ERR_ARG;
@@ -1816,6 +1866,7 @@ int fusedmm_b200_release(void)
    if (cudaGetDevice(&cur) != cudaSuccess) { cudaGetLastError(); return FUSEDMM_B200_ERR_CUDA; }
    for (DeviceCtx &c : g_ctx) {
       if (!c.ready) continue;
+      std::lock_guard<std::mutex> device_lock(c.mu);
       cudaSetDevice(c.device);
       cudaStreamSynchronize(c.stream);
       DevBuf *bufs[] = {&c.stage[0], &c.stage[1], &c.stage[2], &c.stage[3], &c.stage[4], &c.stage[5], &c.stage[6],

@@ -10,8 +10,17 @@ namespace fmm {
 // budget class MB).  G*NV*16 bytes is the longest row a tiling covers.
 #define FMM_FOR_EACH_TILING(X) \
    X(4, 1, 4, 0) X(8, 1, 8, 0) X(8, 2, 4, 0) X(8, 4, 2, 0) X(16, 1, 8, 0) X(16, 2, 4, 0) X(16, 4, 2, 0) \
-   X(32, 1, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 0) X(32, 8, 1, 0) \
+   X(32, 1, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 0) X(32, 8, 1, 0) X(32, 16, 1, 0) \
    X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3) X(16, 2, 4, 3) X(32, 2, 4, 3)
+
+// The default tilings once more for calls whose K fills the tiling exactly (K = G*NV*16 bytes: every power of two
+// from 16 to 2048 floats, 8 to 1024 doubles): FLAG_EXACT_K drops the per-vector bounds predicates of every gather and
+// store.  FR on R-MAT scale 20 at K = 256: 4.01 ms against 4.32; SpMM at K = 512: 27.8 against 28.6.  Two default
+// tilings are left out because their exact forms measured slower: (16, 2, 8) for the chunks at K = 128 floats (R-MAT
+// scale 24: chunk launch 30.5 ms against 25.8) and (8, 2, 4) at K = 64 floats (+1 %).
+#define FMM_FOR_EACH_EXACT_TILING(X) \
+   X(4, 1, 4, 0) X(8, 1, 8, 0) X(16, 2, 4, 3) X(32, 2, 4, 0) X(32, 2, 8, 0) X(32, 2, 4, 3) \
+   X(32, 4, 2, 3) X(32, 8, 1, 0) X(32, 16, 1, 0)
 
 // A translation unit may add tilings of its own by defining this before the include (the flag-interpreting
 // kernels need other register budgets than the specialised ones).
@@ -27,6 +36,11 @@ namespace fmm {
    case ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                                           \
       launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_>, grid,      \
                         warps * 32, stream, p);                                                       \
+      return true;
+#define FMM_EXACT_TILING_CASE(G_, NV_, U_, MB_)                                                      \
+   case (1 << 28) | ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                               \
+      launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_,             \
+                                         FLAG_EXACT_K>, grid, warps * 32, stream, p);                 \
       return true;
 
 // persistent launch of the edge-stream kernel: as many CTAs as fit on the device at once
@@ -58,12 +72,14 @@ namespace fmm {
    {                                                                                                  \
       using T_ = T;                                                                                   \
       constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
-      /* U carries the register budget class MB in bits 8.. (0 = compiler's choice) */                        \
-      const int MB = U >> 8;                                                                          \
+      /* U carries the register budget class MB in bits 8..15 (0 = compiler's choice) and the call-shape   */ \
+      /* flags (FLAG_EXACT_K) in bits 16..                                                                  */ \
+      const int MB = (U >> 8) & 0xFF, FL = (U >> 16) & 1;                                             \
       U &= 0xFF;                                                                                      \
-      switch ((MB << 24) | (U << 16) | (G << 8) | NV) {                                               \
+      switch ((FL << 28) | (MB << 24) | (U << 16) | (G << 8) | NV) {                                  \
          FMM_FOR_EACH_TILING(FMM_TILING_CASE)                                                         \
          FMM_FOR_EACH_EXTRA_TILING(FMM_TILING_CASE)                                                   \
+         FMM_FOR_EACH_EXACT_TILING(FMM_EXACT_TILING_CASE)                                             \
          default: return false;                                                                       \
       }                                                                                               \
    }

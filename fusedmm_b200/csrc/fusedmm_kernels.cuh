@@ -579,6 +579,7 @@ struct VecEngine {
 };
 
 constexpr int WARPS_PER_CTA = 8;  // upper bound; the launch chooses blockDim.x = 32 * (1..8)
+constexpr int ANY_MAX_CACHED = 512;  // element-strided engine: edges of an item whose scalars are kept in shared memory
 
 // One warp per row (MODE_ROWS) or a grid-stride loop over the chunks of split rows
 // (MODE_HUB_CHUNKS).  Rows longer than p.chunk are skipped in MODE_ROWS.
@@ -696,8 +697,9 @@ fused_vec_kernel(const Params<T> p)
 // ---------------------------------------------------------------------------------------------------
 // Element-strided engine: any K, any leading dimension, any alignment; all stage codes at run time.
 // Lane l owns elements l, l+32, ... of a 32*EPT-element tile of K; a message with a reduction walks
-// the whole K once per edge and per tile to get s.  It exists so that every legal call has a GPU
-// path; the vector engine is the fast one.
+// the whole K once per edge to get s, keeps the scalars of the item's edges in shared memory and then walks
+// the tiles (items of more than ANY_MAX_CACHED edges recompute s per tile).  It exists so that every legal
+// call has a GPU path; the vector engine is the fast one.
 // ---------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
@@ -739,6 +741,39 @@ fused_any_kernel(const Params<T> p)
       T *dst = to_z ? p.z + w.row * p.ldz : p.partials + w.dst_item * p.k;
       const bool need_x = vop_reads_x(vop) || rop_reads_x(rop);
 
+      // One edge's scalar: the reduction over ALL of K (or a_uv), then the scalar function.
+      auto edge_scalar = [&](long long j, const T *yr) -> T {
+         T s;
+         if (rop != ROP_NOOP) {
+            s = T(0);
+            for (long long t = lane; t < p.k; t += 32) {
+               const T xe = need_x ? xr[t] : T(0);
+               const T ye = need_y ? __ldg(yr + t) : T(0);
+               s += rop_term(rop, xe, vop_apply(vop, xe, ye));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
+         } else {
+            s = use_val ? __ldg(p.val + j) : T(0);
+         }
+         return use_sop_udef ? sop_udef(s, p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : s;
+      };
+      // When K spans several tiles and the message has a reduction, every tile needs every edge's scalar again:
+      // compute them once and keep them in shared memory (one per edge of the item) instead of walking all of K
+      // once per tile and edge.
+      extern __shared__ __align__(16) unsigned char any_smem[];  // blockDim.x / 32 * ANY_MAX_CACHED values
+      T *mine = reinterpret_cast<T *>(any_smem) + (threadIdx.x >> 5) * ANY_MAX_CACHED;
+      const bool cached = rop != ROP_NOOP && p.k > 32 * EPT && w.ee - w.eb <= ANY_MAX_CACHED;
+      if (cached) {
+         __syncwarp();  // the previous item's scalars are no longer read
+         for (long long j = w.eb; j < w.ee; j++) {
+            const long long cid = need_y ? ld_index(p.indx, j, p.idx64) : 0;
+            const T out = edge_scalar(j, p.y + cid * p.ldy);
+            if (lane == 0) mine[j - w.eb] = out;
+         }
+         __syncwarp();
+      }
+
       for (long long kt = 0; kt < p.k; kt += 32 * EPT) {
          T acc[EPT];
 #pragma unroll
@@ -746,20 +781,7 @@ fused_any_kernel(const Params<T> p)
          for (long long j = w.eb; j < w.ee; j++) {
             const long long cid = need_y ? ld_index(p.indx, j, p.idx64) : 0;
             const T *yr = p.y + cid * p.ldy;
-            T s;
-            if (rop != ROP_NOOP) {
-               s = T(0);
-               for (long long t = lane; t < p.k; t += 32) {
-                  const T xe = need_x ? xr[t] : T(0);
-                  const T ye = need_y ? __ldg(yr + t) : T(0);
-                  s += rop_term(rop, xe, vop_apply(vop, xe, ye));
-               }
-#pragma unroll
-               for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
-            } else {
-               s = use_val ? __ldg(p.val + j) : T(0);
-            }
-            const T out = use_sop_udef ? sop_udef(s, p.sop_kind, p.sp0, p.sp1, p.sp2, p.sop_table) : s;
+            const T out = cached ? mine[j - w.eb] : edge_scalar(j, yr);
 #pragma unroll
             for (int e = 0; e < EPT; e++) {
                const long long t = kt + e * 32 + lane;
@@ -859,11 +881,13 @@ enum : int { PAT_GENERIC = 0, PAT_SIGMOID = 1, PAT_TDIST = 2, PAT_SPMM = 3, PAT_
 // <<<grid, block, 0, stream>>> with, when p.pdl is set, the attribute that lets the kernel overlap its launch with
 // the tail of the kernel before it in the stream.
 template <typename T>
-inline cudaError_t launch_kernel(void (*kern)(const Params<T>), long long grid, int threads, cudaStream_t stream, const Params<T> &p)
+inline cudaError_t launch_kernel(void (*kern)(const Params<T>), long long grid, int threads, cudaStream_t stream, const Params<T> &p,
+                                 size_t dynamic_smem = 0)
 {
    cudaLaunchConfig_t cfg = {};
    cfg.gridDim = dim3(static_cast<unsigned int>(grid));
    cfg.blockDim = dim3(threads);
+   cfg.dynamicSmemBytes = dynamic_smem;
    cfg.stream = stream;
    cudaLaunchAttribute attr[1];
    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -17,6 +17,12 @@
  * it returns, exactly like the reference; when it is given device arrays it first waits for all work
  * already enqueued on the device (cudaDeviceSynchronize), because it runs on a stream of its own.
  *
+ * Threads.  Every entry point may be called from any host thread.  Calls that target the same device (the
+ * device that is current in the calling thread) run one after the other; calls from different threads on
+ * DIFFERENT devices run side by side, so one process can drive several GPUs (one thread per GPU, each with its
+ * own device current and its row shard).  Options and the default SOP are process-wide; a call uses the values
+ * in force when it starts.
+ *
  * There is no CPU implementation in this library.  If no CUDA device is usable every entry point
  * returns FUSEDMM_B200_ERR_CUDA.
  */
@@ -393,10 +399,13 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    a function that differs from the built-in only between or beyond the sample points is not
  *                    told apart.  1: such a hook is not examined and the call returns status 64; SOP_UDEF then
  *                    needs fusedmm_b200_set_sop or an explicit sop argument.
- *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time for
- *                    the shape of the call (exactly this K: no bounds predicates; 32-bit row offsets when column ids
- *                    are 32 bits wide and Y lies within 2^32 elements); 2: every call does.  Bit-identical results;
- *                    measured slower than the built-in kernels on three of four benchmark configurations.
+ *   "exact_k"        1 (default): a call whose k fills its tiling exactly (every power of two from 16 to 2048 floats,
+ *                    8 to 1024 doubles) runs the instantiation without per-vector bounds predicates (7 % faster at
+ *                    k = 256 floats, neutral at 128 and 512; bit-identical results); 0: always the general one.
+ *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time that
+ *                    also uses 32-bit row offsets when column ids are 32 bits wide and Y lies within 2^32 elements;
+ *                    2: every call does.  Bit-identical results; measured 4-50 % slower: an experiment, left off.
+ *   "jit_shape_mask" bit 1 switches the 32-bit row offsets of "jit_call_shape" on (default 3).
  *   "hub_cap_initial"  split rows the hub list has room for when it is first allocated (default 65536; it grows on
  *                    demand, this only sets where the growth starts: tests use it to reach the growth path).
  *   "inject_alloc_failure"  n > 0: the n-th device allocation the library attempts from now on fails
