@@ -193,7 +193,7 @@ struct DeviceCtx {
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, exact_k = 1, hub_cap_initial = 1 << 16;
+           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, exact_k = 1, element_vectors = 1, hub_cap_initial = 1 << 16;
 };
 
 // Locking: g_mu guards the process-wide settings (options, default SOP) and the creation of device contexts; each
@@ -534,7 +534,6 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    const bool async = user_stream != nullptr;
    cudaStream_t st = async ? user_stream : c.stream;
    const size_t es = sizeof(T), ps = a.ptr_bits / 8, is = a.idx_bits / 8;
-   constexpr int W = VecOf<T>::W;
 
    const bool need_x = vop_reads_x(d.vop) || rop_reads_x(d.rop);
    const bool need_y = vop_reads_y(d.vop);
@@ -697,11 +696,17 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
 
    // ---- engine choice ---------------------------------------------------------------------------------
    auto aligned16 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-   bool vec_ok = (a.k % W == 0) && (zld % W == 0) && aligned16(p.z) &&
-                 (!need_x || ((a.ldx % W == 0) && aligned16(p.x))) &&
-                 (!need_y || ((a.ldy % W == 0) && aligned16(p.y)));
+   constexpr int W16 = VecOf<T>::W;  // elements per 16-byte vector
+   bool vec_ok = (a.k % W16 == 0) && (zld % W16 == 0) && aligned16(p.z) &&
+                 (!need_x || ((a.ldx % W16 == 0) && aligned16(p.x))) &&
+                 (!need_y || ((a.ldy % W16 == 0) && aligned16(p.y)));
    for (int i = 0; i < p.n_peers; i++) vec_ok = vec_ok && aligned16(p.z_peer[i]);
    if (p.z_mc) vec_ok = vec_ok && aligned16(p.z_mc);
+   // Rows that are not 16-byte granular (K, a leading dimension or a base address): the same engine with one-element
+   // vectors (FLAG_ELEMENT) as long as a row fits its widest tiling (512 elements); beyond, the element-strided engine.
+   const bool element_mode = !vec_ok && a.k <= 512 && t_opt.element_vectors && t_opt.engine != 2;
+   if (element_mode) vec_ok = true;
+   const int W = element_mode ? 1 : W16;  // elements per vector of the kernels this call launches
    int G = 0, NV = 0, U = 0;
    int Us = 0;  // gathers in flight and register budget of a kernel specialised for the message (U is the flag-interpreting kernel's)
    const int warps = static_cast<int>(std::min<int64_t>(std::max<int64_t>(t_opt.warps_per_cta, 1), WARPS_PER_CTA));
@@ -713,16 +718,17 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          if (U == 0) U = default_u(G, NV);
          U |= static_cast<int>((t_opt.force_tiling >> 24) & 0xFF) << 8;  // register budget class (0 = default)
       } else {
-         choose_tiling(a.k / W, sizeof(T) == 8, &G, &NV, &U);
+         // one-element vectors: the table by elements, float's choices for both value types (one set of instantiations)
+         choose_tiling(a.k / W, sizeof(T) == 8 && !element_mode, &G, &NV, &U);
          Us = U;
-         if (t_opt.force_generic || d.pattern == PAT_GENERIC) tiling_for_generic(G, NV, &U);
+         if ((t_opt.force_generic || d.pattern == PAT_GENERIC) && !element_mode) tiling_for_generic(G, NV, &U);
       }
       if (Us == 0) Us = U;
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
    // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
    int Gr = G, NVr = NV, Ur = U, Urs = Us;  // Urs: U | budget of a specialised kernel for the whole rows
-   if (vec_ok && !t_opt.force_tiling && !t_opt.force_tiling_rows) {
+   if (vec_ok && !element_mode && !t_opt.force_tiling && !t_opt.force_tiling_rows) {
       int g2 = 0, nv2 = 0, u2 = 0;
       if (choose_rows_tiling(a.k / W, sizeof(T) == 8, &g2, &nv2, &u2) && static_cast<long long>(g2) * nv2 * W >= a.k) {
          if (d.pattern != PAT_GENERIC && !t_opt.force_generic) { Gr = g2; NVr = nv2; Ur = u2; Urs = u2; }
@@ -749,8 +755,8 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // A call whose K fills its tiling exactly runs the instantiation without per-vector bounds predicates
    // (FLAG_EXACT_K; compiled in for the default tilings, built at run time for messages outside the four patterns).
    // 32-bit row offsets (FLAG_OFFSET32) exist only as an experiment behind option "jit_call_shape".
-   int jit_flags = 0;
-   if (vec_ok && t_opt.jit_call_shape && t_opt.jit > 0 && !t_opt.force_generic && (jit_weight >= (1ll << 26) || t_opt.jit_call_shape == 2)) {
+   int jit_flags = element_mode ? FLAG_ELEMENT : 0;
+   if (vec_ok && !element_mode && t_opt.jit_call_shape && t_opt.jit > 0 && !t_opt.force_generic && (jit_weight >= (1ll << 26) || t_opt.jit_call_shape == 2)) {
       const bool need_y_ = vop_reads_y(d.vop);
       if (need_y_ && a.idx_bits == 32 && a.n > 0 && static_cast<double>(a.n - 1) * static_cast<double>(a.ldy) + static_cast<double>(a.k) <= 4294967295.0)
          jit_flags |= FLAG_OFFSET32;
@@ -759,7 +765,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    }
    bool jit_used = false;
    auto launch_main = [&](const Params<T> &q, int g, int nv, int u_rt, int u_special, int w, long long grid, cudaStream_t s) -> bool {
-      const bool ex = t_opt.exact_k && static_cast<long long>(g) * nv * W == a.k;  // per launch: the whole rows may have their own tiling
+      const bool ex = t_opt.exact_k && !element_mode && static_cast<long long>(g) * nv * W == a.k;  // per launch: the whole rows may have their own tiling
       const int fl = (jit_flags & ~FLAG_EXACT_K) | (ex ? FLAG_EXACT_K : 0);
       if (jit_policy > 0 && jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_special & 0xFF,
                                               jit_budget(g, nv, u_special & 0xFF, u_special >> 8), fl, w, q, grid, s, jit_policy,
@@ -774,11 +780,12 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          if (launch_vec<T>(pattern, g, nv, u_budget | (1 << 16), w, q, grid, s)) return true;
          if (launch_vec<T>(pattern, g, nv, u_rt | (1 << 16), w, q, grid, s)) return true;
       }
-      if (launch_vec<T>(pattern, g, nv, u_rt, w, q, grid, s)) return true;
+      if (launch_vec<T>(pattern, g, nv, u_rt | (element_mode ? (2 << 16) : 0), w, q, grid, s)) return true;
       // a tiling (option force_tiling / force_tiling_rows) that is not among the instantiations compiled into the
       // library: build it at run time
       if (t_opt.jit > 0 && g > 0 && 32 % g == 0 && nv > 0 && (u_rt & 0xFF) > 0 &&
-          jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_rt & 0xFF, u_rt >> 8, 0, w, q, grid, s, 2, jit_weight)) {
+          jit_launch_vec<T>(d.vop, d.rop, d.vsc, d.aop, g, nv, u_rt & 0xFF, u_rt >> 8, element_mode ? FLAG_ELEMENT : 0, w, q, grid, s, 2,
+                            jit_weight)) {
          jit_used = true;
          return true;
       }
@@ -1778,6 +1785,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "hub_cap_initial")) return &g_opt.hub_cap_initial;
    if (!strcmp(name, "jit_shape_mask")) return &g_opt.jit_shape_mask;
    if (!strcmp(name, "exact_k")) return &g_opt.exact_k;
+   if (!strcmp(name, "element_vectors")) return &g_opt.element_vectors;
    if (!strcmp(name, "timing_detail")) return &g_opt.timing_detail;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
@@ -1813,7 +1821,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    int64_t *s = option_slot(name);
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.force_generic && value > 2) return FUSEDMM_B200_ERR_ARG;
-   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail || s == &g_opt.exact_k) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail || s == &g_opt.exact_k || s == &g_opt.element_vectors) && value > 1) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if ((s == &g_opt.engine || s == &g_opt.jit || s == &g_opt.jit_call_shape) && value > 2) return FUSEDMM_B200_ERR_ARG;

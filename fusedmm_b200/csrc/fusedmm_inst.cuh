@@ -22,6 +22,11 @@ namespace fmm {
    X(4, 1, 4, 0) X(8, 1, 8, 0) X(16, 2, 4, 3) X(32, 2, 4, 0) X(32, 2, 8, 0) X(32, 2, 4, 3) \
    X(32, 4, 2, 3) X(32, 8, 1, 0) X(32, 16, 1, 0)
 
+// The default tilings with one-element vectors (FLAG_ELEMENT), for calls whose K, leading dimensions or base addresses
+// are not multiples of 16 bytes: K up to G*NV elements (512); 2-D / 3-D layouts (K = 2, 3) get 8 rows per warp.
+#define FMM_FOR_EACH_ELEMENT_TILING(X) \
+   X(4, 1, 4, 0) X(8, 1, 8, 0) X(8, 2, 4, 4) X(16, 2, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 3) X(32, 8, 1, 0) X(32, 16, 1, 0)
+
 // A translation unit may add tilings of its own by defining this before the include (the flag-interpreting
 // kernels need other register budgets than the specialised ones).
 #ifndef FMM_FOR_EACH_EXTRA_TILING
@@ -36,6 +41,11 @@ namespace fmm {
    case ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                                           \
       launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_>, grid,      \
                         warps * 32, stream, p);                                                       \
+      return true;
+#define FMM_ELEMENT_TILING_CASE(G_, NV_, U_, MB_)                                                    \
+   case (2 << 28) | ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                               \
+      launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_,             \
+                                         FLAG_ELEMENT>, grid, warps * 32, stream, p);                 \
       return true;
 #define FMM_EXACT_TILING_CASE(G_, NV_, U_, MB_)                                                      \
    case (1 << 28) | ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                               \
@@ -73,13 +83,14 @@ namespace fmm {
       using T_ = T;                                                                                   \
       constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
       /* U carries the register budget class MB in bits 8..15 (0 = compiler's choice) and the call-shape   */ \
-      /* flags (FLAG_EXACT_K) in bits 16..                                                                  */ \
-      const int MB = (U >> 8) & 0xFF, FL = (U >> 16) & 1;                                             \
+      /* flags in bits 16..: 1 = FLAG_EXACT_K, 2 = FLAG_ELEMENT (never both here)                         */ \
+      const int MB = (U >> 8) & 0xFF, FL = (U >> 16) & 3;                                             \
       U &= 0xFF;                                                                                      \
       switch ((FL << 28) | (MB << 24) | (U << 16) | (G << 8) | NV) {                                  \
          FMM_FOR_EACH_TILING(FMM_TILING_CASE)                                                         \
          FMM_FOR_EACH_EXTRA_TILING(FMM_TILING_CASE)                                                   \
          FMM_FOR_EACH_EXACT_TILING(FMM_EXACT_TILING_CASE)                                             \
+         FMM_FOR_EACH_ELEMENT_TILING(FMM_ELEMENT_TILING_CASE)                                         \
          default: return false;                                                                       \
       }                                                                                               \
    }

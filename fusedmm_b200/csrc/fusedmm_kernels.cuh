@@ -154,6 +154,15 @@ __device__ __forceinline__ void st_vec(T *ptr, const T (&in)[VecOf<T>::W])
    *reinterpret_cast<V *>(ptr) = v;
 }
 
+// One-element "vectors" (FLAG_ELEMENT: K, a leading dimension or a base address that is not a multiple of 16 bytes):
+// the same engine with 4- or 8-byte accesses, a warp instruction still covers one contiguous G-element piece of a row.
+__device__ __forceinline__ void ld_vec_nc(const float *ptr, float (&out)[1]) { out[0] = __ldg(ptr); }
+__device__ __forceinline__ void ld_vec_nc(const double *ptr, double (&out)[1]) { out[0] = __ldg(ptr); }
+__device__ __forceinline__ void ld_vec(const float *ptr, float (&out)[1]) { out[0] = *ptr; }
+__device__ __forceinline__ void ld_vec(const double *ptr, double (&out)[1]) { out[0] = *ptr; }
+__device__ __forceinline__ void st_vec(float *ptr, const float (&in)[1]) { *ptr = in[0]; }
+__device__ __forceinline__ void st_vec(double *ptr, const double (&in)[1]) { *ptr = in[0]; }
+
 // multimem.st: one store through an NVSwitch multicast address lands in every GPU's copy of the buffer
 __device__ __forceinline__ void st_vec_multicast(float *mc, const float (&in)[4])
 {
@@ -182,6 +191,9 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 // Lets the next kernel in the stream (if it was launched that way) become resident now instead of when this grid
 // has drained; it still waits for this grid's completion in grid_dependency_wait.
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+__device__ __forceinline__ void st_vec_multicast(float *mc, const float (&in)[1]) { st_multicast(mc, in[0]); }
+__device__ __forceinline__ void st_vec_multicast(double *mc, const double (&in)[1]) { st_multicast(mc, in[0]); }
 
 template <typename T> __device__ __forceinline__ T pos_inf();
 template <> __device__ __forceinline__ float  pos_inf<float>()  { return __int_as_float(0x7f800000); }
@@ -415,12 +427,14 @@ __device__ __forceinline__ void reduce_hub_row(const Params<T> &p, long long row
 //                  predicates on every gather and store go away;
 //   FLAG_OFFSET32  column ids are 32 bits wide and every element offset into Y (cid*ldy + k) is below 2^32: the row
 //                  offset is one 32x32->64-bit multiply-add instead of a 64-bit multiply per edge.
-// The kernels compiled into the library use FLAGS = 0 and take every call.
-enum : int { FLAG_EXACT_K = 1, FLAG_OFFSET32 = 2 };
+//   FLAG_ELEMENT   vectors of ONE element instead of 16 bytes: for calls whose K, leading dimensions or base addresses
+//                  are not multiples of 16 bytes (K up to G*NV elements).
+// FLAGS = 0 takes every call whose rows are 16-byte granular.
+enum : int { FLAG_EXACT_K = 1, FLAG_OFFSET32 = 2, FLAG_ELEMENT = 4 };
 
 template <typename T, int VOPC, int ROPC, int VSCC, int AOPC, int G, int NV, int U, int FLAGS = 0>
 struct VecEngine {
-   static constexpr int W = VecOf<T>::W;
+   static constexpr int W = (FLAGS & FLAG_ELEMENT) ? 1 : VecOf<T>::W;
    static constexpr bool EXACT_K = (FLAGS & FLAG_EXACT_K) != 0;
    static constexpr bool OFFSET32 = (FLAGS & FLAG_OFFSET32) != 0;
    static constexpr int S = 32 / G;  // edge slots per warp

@@ -402,6 +402,9 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *   "exact_k"        1 (default): a call whose k fills its tiling exactly (every power of two from 16 to 2048 floats,
  *                    8 to 1024 doubles) runs the instantiation without per-vector bounds predicates (7 % faster at
  *                    k = 256 floats, neutral at 128 and 512; bit-identical results); 0: always the general one.
+ *   "element_vectors"  1 (default): a call whose k, leading dimensions or base addresses are not multiples of 16 bytes
+ *                    and whose k is at most 512 runs the vector engine with one-element vectors (4- or 8-byte
+ *                    accesses); 0: such calls take the element-strided engine, as rows longer than 512 elements do.
  *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time that
  *                    also uses 32-bit row offsets when column ids are 32 bits wide and Y lies within 2^32 elements;
  *                    2: every call does.  Bit-identical results; measured 4-50 % slower: an experiment, left off.

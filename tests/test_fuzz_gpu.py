@@ -1,6 +1,6 @@
 """Seeded fuzzing of the C ABI against the CPU oracle: random messages (every valid stage code), shapes down to
 one row / one column / no edges at all, padded leading dimensions, all index-width combinations, both value
-types, both schedulers, host and device arrays, beta 0 and 1."""
+types, both schedulers, all engines, host and device arrays, beta 0 and 1."""
 import numpy as np
 import pytest
 
@@ -51,7 +51,9 @@ def one_case(rng, device, oracle, case):
                       zero_first=not generic)
     use_stream_engine = contiguous and rng.random() < 0.5
     host = rng.random() < 0.35
+    element_vectors = int(rng.random() < 0.6)   # rows that are not 16-byte granular: one-element vectors, or the element-strided engine
     api.set_option("engine", 2 if use_stream_engine else 0)
+    api.set_option("element_vectors", element_vectors)
     try:
         if host:
             z = z0.copy()
@@ -73,6 +75,7 @@ def one_case(rng, device, oracle, case):
             z = t["z"].cpu().numpy()
     finally:
         api.set_option("engine", 0)
+        api.set_option("element_vectors", 1)
     tag = (case, hex(msg), m, n, k, (ldx, ldy, ldz), vt.__name__, pt.__name__, it.__name__, sop, beta, hub, contiguous,
            use_stream_engine, host)
     assert st == st_o == 0, tag
@@ -92,16 +95,18 @@ def one_case(rng, device, oracle, case):
 
         ok, e, e_gpu, e_or = within_tolerance(z, want, RTOL[np.dtype(vt)], exact, k)
         assert ok, (tag, e, e_gpu, e_or)
-        return 1, int(info.engine == 2), int(info.lanes_per_edge == 0)
-    return 0, 0, 0
+        w = 16 // np.dtype(vt).itemsize
+        granular = k % w == 0 and ldx % w == 0 and ldy % w == 0 and ldz % w == 0
+        return 1, int(info.engine == 2), int(info.lanes_per_edge == 0), int(info.lanes_per_edge > 0 and not granular)
+    return 0, 0, 0, 0
 
 
 @pytest.mark.parametrize("seed", [20240607, 7, 99])
 def test_fuzz_against_the_oracle(cuda_device, oracle, seed):
     rng = np.random.default_rng(seed)
-    compared = stream = strided = 0
+    compared = stream = strided = element = 0
     for case in range(1500):
-        c, s, a = one_case(rng, cuda_device, oracle, case)
-        compared, stream, strided = compared + c, stream + s, strided + a
-    # nearly every case has a finite reference result, and all three engines were exercised many times
-    assert compared >= 1350 and stream >= 100 and strided >= 300, (compared, stream, strided)
+        c, s, a, e = one_case(rng, cuda_device, oracle, case)
+        compared, stream, strided, element = compared + c, stream + s, strided + a, element + e
+    # nearly every case has a finite reference result, and all engines were exercised many times
+    assert compared >= 1350 and stream >= 100 and strided >= 150 and element >= 150, (compared, stream, strided, element)

@@ -249,15 +249,21 @@ def test_m_smaller_than_rows_and_unaligned_views(cuda_device, oracle):
     zc = z.cpu().numpy()
     assert rel_err(zc[r0:r0 + m], want[r0:r0 + m]) <= 1e-4
     assert (zc[:r0] == 9.0).all() and (zc[r0 + m:] == 9.0).all()
-    # a Y that starts 4 bytes off a 16-byte boundary cannot use 16-byte loads: element-strided engine
+    # a Y that starts 4 bytes off a 16-byte boundary cannot use 16-byte loads: the vector engine with one-element
+    # vectors, or (option element_vectors = 0) the element-strided engine
     ybig = torch.zeros(n * k + 1, device=cuda_device)
     yoff = ybig[1:].view(n, k)
     yoff.copy_(t["y"])
-    z2 = torch.zeros((rows, k), device=cuda_device)
-    assert api.fusedMM_csr(M.MSG_SPMM, m, n, k, 1.0, 0, rows, n, t["val"], t["indx"], t["pb"][r0:], t["pe"][r0:],
-                           t["x"][r0:], k, yoff, k, 0.0, z2[r0:], k) == 0
-    assert api.call_info().lanes_per_edge == 0
-    assert rel_err(z2.cpu().numpy()[r0:r0 + m], want[r0:r0 + m]) <= 1e-4
+    for element_vectors in (1, 0):
+        api.set_option("element_vectors", element_vectors)
+        try:
+            z2 = torch.zeros((rows, k), device=cuda_device)
+            assert api.fusedMM_csr(M.MSG_SPMM, m, n, k, 1.0, 0, rows, n, t["val"], t["indx"], t["pb"][r0:], t["pe"][r0:],
+                                   t["x"][r0:], k, yoff, k, 0.0, z2[r0:], k) == 0
+            assert (api.call_info().lanes_per_edge > 0) == bool(element_vectors)
+        finally:
+            api.set_option("element_vectors", 1)
+        assert rel_err(z2.cpu().numpy()[r0:r0 + m], want[r0:r0 + m]) <= 1e-4
 
 
 def test_caller_supplied_sop_udef_func_is_recognised(cuda_device, oracle):
@@ -576,6 +582,52 @@ def test_kernels_built_for_the_shape_of_a_call(cuda_device, oracle, tmp_path, mo
         api.set_option("jit", 1)
         api.set_option("exact_k", 1)
     assert seen >= 20
+
+
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_rows_that_are_not_16_byte_granular(cuda_device, oracle, vt):
+    """K, leading dimensions or bases that are not multiples of 16 bytes (K = 2 and 3 are graph layouts in the plane
+    and in space): the vector engine with one-element vectors for K <= 512, every message kind, split rows, padded
+    leading dimensions, against the oracle."""
+    rng = np.random.default_rng(55)
+    m, n = 1300, 1100
+    for k, ldpad in ((1, 0), (2, 0), (3, 1), (7, 0), (30, 3), (67, 0), (250, 1), (511, 0), (512, 1)):
+        ld = k + ldpad
+        pntrb, pntre, indx, val = random_csr(rng, m, n, 8, np.int64, np.int32, hub=1500)
+        val = val.astype(vt)
+        x, y = np.nan_to_num(dense(rng, m, k, ld, vt)), np.nan_to_num(dense(rng, n, k, ld, vt))
+        for name in ("sigmoid", "tdist", "spmm", "gcn", "add_addrhs_vscadd_add", "max_dot_copy_mul_min"):
+            msg, sop = MESSAGES[name], sop_for(name)
+            generic = msg not in (M.MSG_SIGMOID, M.MSG_TDIST, M.MSG_SPMM, M.MSG_GCN)
+            z0 = rng.uniform(-1, 1, size=(m, ld)).astype(vt) if generic else np.zeros((m, ld), vt)
+            want = z0.copy()
+            assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, ld, y, ld, 0.0, want, ld, sop_kind=sop,
+                              zero_first=not generic) == 0
+            st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, ld, y, ld, 0.0, z0.copy(), ld, sop=sop)
+            info = api.call_info()
+            granular = k % (16 // np.dtype(vt).itemsize) == 0 and ld % (16 // np.dtype(vt).itemsize) == 0
+            assert st == 0 and info.lanes_per_edge > 0 and info.hub_rows >= 1, (name, k, ld)
+            assert granular or info.lanes_per_edge * info.vectors_per_lane >= k   # one element per vector
+            assert np.array_equal(z[:, k:], z0[:, k:])                                # padding columns untouched
+
+            def exact():
+                if vt == np.float32:
+                    ex = z0.astype(np.float64)
+                    oracle.csr(msg, m, n, k, val.astype(np.float64), indx, pntrb, pntre, x.astype(np.float64), ld,
+                               y.astype(np.float64), ld, 0.0, ex, ld, sop_kind=sop, zero_first=not generic)
+                    return ex
+                from oracle.cpu import numpy_fusedmm
+                return numpy_fusedmm(msg, m, k, val, indx, pntrb, pntre, x, y, z0, sop_kind=sop, dtype=np.longdouble)
+
+            ok, e, e_gpu, e_or = within_tolerance(z, want, RTOL[np.dtype(vt)], exact, k)
+            assert ok, (name, k, ld, e, e_gpu, e_or)
+    # longer rows than the widest tiling of one-element vectors: the element-strided engine
+    k = 515
+    x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+    want = np.zeros((m, k), vt)
+    oracle.csr(M.MSG_TDIST, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=M.SOP_TDIST)
+    st, z = run_gpu(cuda_device, M.MSG_TDIST, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, np.zeros((m, k), vt), k, sop=M.SOP_TDIST)
+    assert st == 0 and api.call_info().lanes_per_edge == 0 and rel_err(z, want) <= RTOL[np.dtype(vt)]
 
 
 def test_async_stream_entry(cuda_device, oracle):
