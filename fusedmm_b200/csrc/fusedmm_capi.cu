@@ -41,7 +41,9 @@ namespace fmm {
    bool launch_vec_##PN##_f32(int, int, int, int, const Params<float> &, long long, cudaStream_t);    \
    bool launch_vec_##PN##_f64(int, int, int, int, const Params<double> &, long long, cudaStream_t);   \
    bool launch_vec_##PN##_f32_stream(int, int, int, const Params<float> &, int, cudaStream_t);        \
-   bool launch_vec_##PN##_f64_stream(int, int, int, const Params<double> &, int, cudaStream_t);
+   bool launch_vec_##PN##_f64_stream(int, int, int, const Params<double> &, int, cudaStream_t);       \
+   bool launch_vec_##PN##_f32_bulk(int, int, int, int, const Params<float> &, int, int, cudaStream_t); \
+   bool launch_vec_##PN##_f64_bulk(int, int, int, int, const Params<double> &, int, int, cudaStream_t);
 FMM_DECLARE_LAUNCHER(generic)
 FMM_DECLARE_LAUNCHER(sigmoid)
 FMM_DECLARE_LAUNCHER(tdist)
@@ -68,6 +70,30 @@ bool launch_vec<double>(int pattern, int G, int NV, int U, int warps, const Para
       case PAT_SPMM:    return launch_vec_spmm_f64(G, NV, U, warps, p, grid, s);
       case PAT_GCN:     return launch_vec_gcn_f64(G, NV, U, warps, p, grid, s);
       default:          return launch_vec_generic_f64(G, NV, U, warps, p, grid, s);
+   }
+}
+template <typename T>
+bool launch_bulk(int pattern, int G, int NV, int D, int warps, const Params<T> &p, int sm_count, int max_per_sm, cudaStream_t s);
+template <>
+bool launch_bulk<float>(int pattern, int G, int NV, int D, int warps, const Params<float> &p, int sm_count, int max_per_sm, cudaStream_t s)
+{
+   switch (pattern) {
+      case PAT_SIGMOID: return launch_vec_sigmoid_f32_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      case PAT_TDIST:   return launch_vec_tdist_f32_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      case PAT_SPMM:    return launch_vec_spmm_f32_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      case PAT_GCN:     return launch_vec_gcn_f32_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      default:          return false;
+   }
+}
+template <>
+bool launch_bulk<double>(int pattern, int G, int NV, int D, int warps, const Params<double> &p, int sm_count, int max_per_sm, cudaStream_t s)
+{
+   switch (pattern) {
+      case PAT_SIGMOID: return launch_vec_sigmoid_f64_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      case PAT_TDIST:   return launch_vec_tdist_f64_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      case PAT_SPMM:    return launch_vec_spmm_f64_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      case PAT_GCN:     return launch_vec_gcn_f64_bulk(G, NV, D, warps, p, sm_count, max_per_sm, s);
+      default:          return false;
    }
 }
 template <typename T>
@@ -193,7 +219,7 @@ struct DeviceCtx {
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
            engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, exact_k = 1, element_vectors = 1, hub_cap_initial = 1 << 16;
+           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, exact_k = 1, element_vectors = 1, bulk_chunks = 0, bulk_warps = 8, bulk_ctas_per_sm = 0, hub_cap_initial = 1 << 16;
 };
 
 // Locking: g_mu guards the process-wide settings (options, default SOP) and the creation of device contexts; each
@@ -274,6 +300,7 @@ int get_ctx(DeviceCtx **out)
       for (auto &e : c.ev_block) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
       CK(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
       CKI(ensure_buf(c.counter, 256));
+      CK(cudaMemset(c.counter.ptr, 0, 256));
       c.ready = true;
    }
    *out = &c;
@@ -749,12 +776,10 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // option "jit" says it is worth it; otherwise, or when that fails, the flag-interpreting instantiation runs.
    const long long jit_weight = a.nnz > 0 && a.nnz < (1ll << 40) ? a.nnz * a.k : 0;
    int jit_policy = ((d.pattern == PAT_GENERIC && !t_opt.force_generic) || t_opt.force_generic == 2) ? static_cast<int>(t_opt.jit) : 0;
-   // Option "jit_call_shape": a large call of ANY message (the four patterns included) gets a kernel built for the
-   // shape of the call too: exactly this K (no bounds predicates on the vectors of a row) and, when column ids are
-   // 32 bits wide and all of Y lies within 2^32 elements, 32-bit row offsets.
-   // A call whose K fills its tiling exactly runs the instantiation without per-vector bounds predicates
-   // (FLAG_EXACT_K; compiled in for the default tilings, built at run time for messages outside the four patterns).
-   // 32-bit row offsets (FLAG_OFFSET32) exist only as an experiment behind option "jit_call_shape".
+   // Flags of the CALL that pick a variant of the kernel (fusedmm_kernels.cuh): FLAG_ELEMENT for rows that are not
+   // 16-byte granular; FLAG_EXACT_K, decided per launch in launch_main, when K fills the tiling exactly (compiled in
+   // for the default tilings, built at run time for messages outside the four patterns); FLAG_OFFSET32 (32-bit row
+   // offsets) only as an experiment behind option "jit_call_shape", always through a kernel built at run time.
    int jit_flags = element_mode ? FLAG_ELEMENT : 0;
    if (vec_ok && !element_mode && t_opt.jit_call_shape && t_opt.jit > 0 && !t_opt.force_generic && (jit_weight >= (1ll << 26) || t_opt.jit_call_shape == 2)) {
       const bool need_y_ = vop_reads_y(d.vop);
@@ -763,7 +788,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       jit_flags &= static_cast<int>(t_opt.jit_shape_mask);
       if (jit_flags & FLAG_OFFSET32) jit_policy = std::max<int>(jit_policy, static_cast<int>(t_opt.jit));
    }
-   bool jit_used = false;
+   bool jit_used = false, bulk_used = false;
    auto launch_main = [&](const Params<T> &q, int g, int nv, int u_rt, int u_special, int w, long long grid, cudaStream_t s) -> bool {
       const bool ex = t_opt.exact_k && !element_mode && static_cast<long long>(g) * nv * W == a.k;  // per launch: the whole rows may have their own tiling
       const int fl = (jit_flags & ~FLAG_EXACT_K) | (ex ? FLAG_EXACT_K : 0);
@@ -801,6 +826,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    const bool contiguous_rows = static_cast<const char *>(dv[3]) == static_cast<const char *>(dv[2]) + ps;
    const bool use_stream = vec_ok && contiguous_rows && t_opt.engine == 2 && p.n_peers == 0 && !p.z_mc && !a.plan && NV <= 8;
    p.counter = static_cast<unsigned long long *>(c.counter.ptr);
+   p.error = static_cast<unsigned long long *>(c.counter.ptr) + 12;  // word 12 of the counter block: "a bounded wait ran out"
 
    if (use_stream) {
       // ---- edge-stream scheduler: partition, main kernel, fix-up ------------------------------------
@@ -911,8 +937,18 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       if (detail) CK(cudaEventRecord(c.evk[2], side));
       q.mode = MODE_HUB_CHUNKS;
       q.pdl = pdl && !a.plan && !detail;
-      if (vec_ok) { if (!launch_main(q, G, NV, U, Us, WARPS_PER_CTA, hub_grid, side)) return FUSEDMM_B200_ERR_ARG; }
-      else launch_any<T>(q, WARPS_PER_CTA, hub_grid, side);
+      bool chunks_launched = false;
+      if (vec_ok && !element_mode && t_opt.bulk_chunks && need_y && pattern != PAT_GENERIC) {
+         // option bulk_chunks: neighbour rows staged through shared memory by bulk copies (fusedmm_bulk.cuh)
+         const int bw = static_cast<int>(std::min<int64_t>(std::max<int64_t>(t_opt.bulk_warps, 1), WARPS_PER_CTA));
+         chunks_launched = launch_bulk<T>(pattern, G, NV, static_cast<int>(t_opt.bulk_chunks), bw, q, c.sm_count,
+                                          static_cast<int>(t_opt.bulk_ctas_per_sm), side);
+         bulk_used = bulk_used || chunks_launched;
+      }
+      if (!chunks_launched) {
+         if (vec_ok) { if (!launch_main(q, G, NV, U, Us, WARPS_PER_CTA, hub_grid, side)) return FUSEDMM_B200_ERR_ARG; }
+         else launch_any<T>(q, WARPS_PER_CTA, hub_grid, side);
+      }
       if (detail) CK(cudaEventRecord(c.evk[3], side));
       q.pdl = pdl && !detail;
       launch_fixup<T>(q, c.sm_count, side);
@@ -1035,6 +1071,15 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       CK(cudaEventElapsedTime(&t, c.evk[0], c.ev1)); ms_main += t;
       nh = static_cast<long long>(packed >> HUB_SHIFT);
       nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
+      if (bulk_used) {  // a bounded wait of the bulk-copy kernel ran out: its result cannot be trusted
+         unsigned long long err = 0;
+         CK(cudaMemcpy(&err, p.error, sizeof(err), cudaMemcpyDeviceToHost));
+         if (err) {
+            CK(cudaMemset(p.error, 0, sizeof(err)));
+            fprintf(stderr, "fusedmm_b200: a bulk copy did not complete within its wait limit\n");
+            return FUSEDMM_B200_ERR_CUDA;
+         }
+      }
       if (nh <= p.hub_cap && nchunks <= p.chunk_cap) break;
       if (attempt == 2) return FUSEDMM_B200_ERR_LIMIT;
       // scratch was too small: the chunk and fix-up passes did nothing.  Enlarge and redo them.
@@ -1786,6 +1831,9 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "jit_shape_mask")) return &g_opt.jit_shape_mask;
    if (!strcmp(name, "exact_k")) return &g_opt.exact_k;
    if (!strcmp(name, "element_vectors")) return &g_opt.element_vectors;
+   if (!strcmp(name, "bulk_chunks")) return &g_opt.bulk_chunks;
+   if (!strcmp(name, "bulk_warps")) return &g_opt.bulk_warps;
+   if (!strcmp(name, "bulk_ctas_per_sm")) return &g_opt.bulk_ctas_per_sm;
    if (!strcmp(name, "timing_detail")) return &g_opt.timing_detail;
    if (!strcmp(name, "inject_alloc_failure")) return &g_fail_alloc_in;
    return nullptr;
@@ -1822,6 +1870,8 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    if (!s || value < 0) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.force_generic && value > 2) return FUSEDMM_B200_ERR_ARG;
    if ((s == &g_opt.beta_mode || s == &g_opt.accept_vop_noop || s == &g_opt.side_priority || s == &g_opt.strict_udef || s == &g_opt.multi_skip_empty_rows || s == &g_opt.pdl || s == &g_opt.timing_detail || s == &g_opt.exact_k || s == &g_opt.element_vectors) && value > 1) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.bulk_chunks && value != 0 && value != 16 && value != 32) return FUSEDMM_B200_ERR_ARG;
+   if (s == &g_opt.bulk_warps && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.hub_chunk && (value < 32 || value > (1ll << 30))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if ((s == &g_opt.engine || s == &g_opt.jit || s == &g_opt.jit_call_shape) && value > 2) return FUSEDMM_B200_ERR_ARG;

@@ -3,6 +3,7 @@
 #pragma once
 #include "fusedmm_kernels.cuh"
 #include "fusedmm_stream.cuh"
+#include "fusedmm_bulk.cuh"
 
 namespace fmm {
 
@@ -68,7 +69,36 @@ namespace fmm {
       return true;                                                                                    \
    }
 
+// Chunk launch through bulk copies (fusedmm_bulk.cuh): (G, NV, U, ring slots D).
+#define FMM_FOR_EACH_BULK_TILING(X) \
+   X(8, 2, 4, 16) X(8, 2, 4, 32) X(16, 2, 4, 16) X(16, 2, 4, 32) X(32, 2, 4, 16) X(32, 2, 4, 32) X(32, 4, 2, 16) X(32, 4, 2, 32)
+
+// persistent launch: as many CTAs as fit at once (the ring of every warp lives in dynamic shared memory)
+#define FMM_BULK_CASE(G_, NV_, U_, D_)                                                               \
+   case ((D_) << 16) | ((G_) << 8) | (NV_): {                                                         \
+      auto kern = fused_bulk_chunk_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, D_, 0>;        \
+      const size_t smem = static_cast<size_t>(warps) * (D_) * ((G_) * (NV_) * 16 + 8);                \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                     \
+                               static_cast<int>(smem)) != cudaSuccess) { cudaGetLastError(); return false; } \
+      int per_sm = 0;                                                                                 \
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, warps * 32, smem)              \
+             != cudaSuccess || per_sm < 1) { cudaGetLastError(); return false; }                      \
+      if (max_per_sm > 0 && per_sm > max_per_sm) per_sm = max_per_sm;                                 \
+      return launch_kernel<T_>(kern, static_cast<long long>(sm_count) * per_sm, warps * 32, stream, p, smem) == cudaSuccess; \
+   }
+
 #define FMM_DEFINE_PATTERN_LAUNCHER(FN, T, VOPC, ROPC, VSCC, AOPC)                                   \
+   bool FN##_bulk(int G, int NV, int D, int warps, const Params<T> &p, int sm_count, int max_per_sm,   \
+                  cudaStream_t stream)                                                                \
+   {                                                                                                  \
+      using T_ = T;                                                                                   \
+      constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
+      if (VOPC_ < 0) return false; /* the flag-interpreting instantiation has no bulk form */         \
+      switch ((D << 16) | (G << 8) | NV) {                                                            \
+         FMM_FOR_EACH_BULK_TILING(FMM_BULK_CASE)                                                      \
+         default: return false;                                                                       \
+      }                                                                                               \
+   }                                                                                                  \
    bool FN##_stream(int G, int NV, int warps, const Params<T> &p, int sm_count, cudaStream_t stream)  \
    {                                                                                                  \
       using T_ = T;                                                                                   \

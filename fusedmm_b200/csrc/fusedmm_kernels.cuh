@@ -92,6 +92,7 @@ struct Params {
    // 1: rows without edges are not sent to the other GPUs (every GPU holds the row pointers and zeroes, or
    // keeps, those rows of its own copy itself: zero_empty_rows_kernel); their result is stored locally only
    int skip_empty_remote;
+   unsigned long long *error;    // set to 1 by a kernel whose bounded wait ran out (fusedmm_bulk.cuh); read by the host
    // host side only: launch this kernel with programmatic stream serialization (it may become resident while the
    // kernel before it in the stream is still running and waits at grid_dependency_wait for that kernel's results)
    int pdl;

@@ -405,6 +405,11 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *   "element_vectors"  1 (default): a call whose k, leading dimensions or base addresses are not multiples of 16 bytes
  *                    and whose k is at most 512 runs the vector engine with one-element vectors (4- or 8-byte
  *                    accesses); 0: such calls take the element-strided engine, as rows longer than 512 elements do.
+ *   "bulk_chunks"    0 (default): the chunks of split rows gather neighbour rows with per-lane 16-byte loads; 16 or 32:
+ *                    with bulk asynchronous copies into a shared-memory ring of that many rows per warp
+ *                    (fusedmm_b200/csrc/fusedmm_bulk.cuh; the four optimised messages only).  Same results; measured
+ *                    15 % to 2.4x slower on the benchmark configurations.  "bulk_warps" (1..8, default 8): warps per
+ *                    block of that launch; "bulk_ctas_per_sm" (0 = as many as fit).
  *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time that
  *                    also uses 32-bit row offsets when column ids are 32 bits wide and Y lies within 2^32 elements;
  *                    2: every call does.  Bit-identical results; measured 4-50 % slower: an experiment, left off.

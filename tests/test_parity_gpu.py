@@ -630,6 +630,44 @@ def test_rows_that_are_not_16_byte_granular(cuda_device, oracle, vt):
     assert st == 0 and api.call_info().lanes_per_edge == 0 and rel_err(z, want) <= RTOL[np.dtype(vt)]
 
 
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_chunk_launch_through_bulk_copies(cuda_device, oracle, vt):
+    """Option bulk_chunks: the chunks of split rows gather their neighbour rows with bulk asynchronous copies into a
+    shared-memory ring (fusedmm_bulk.cuh) instead of per-lane loads.  Same result as the default path bit for bit
+    (same lane tiling, same order of additions) and within the tolerance of the oracle; ring of 16 and of 32 rows,
+    blocks of 4 and 8 warps, K filling the tiling and ragged, chunks shorter and longer than the ring."""
+    rng = np.random.default_rng(77)
+    m, n = 900, 800
+    w = 4 if vt == np.float32 else 2
+    try:
+        for k in (16 * w, 32 * w, 64 * w, 128 * w, 64 * w - w):
+            pntrb, pntre, indx, val = random_csr(rng, m, n, 6, np.int64, np.int32, hub=2300)
+            deg = pntre - pntrb
+            deg_extra = np.where(deg > 0)[0][:6]
+            val = val.astype(vt)
+            x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+            for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_TDIST, M.SOP_FR), (M.MSG_SPMM, 0), (M.MSG_GCN, 0)):
+                want = np.zeros((m, k), vt)
+                assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop) == 0
+                api.set_option("bulk_chunks", 0)
+                st0, z_ref = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, np.zeros((m, k), vt), k, sop=sop)
+                assert st0 == 0
+                for d, warps, chunk in ((16, 8, 256), (32, 4, 256), (32, 8, 40), (16, 2, 70)):
+                    api.set_option("bulk_chunks", d)
+                    api.set_option("bulk_warps", warps)
+                    api.set_option("hub_chunk", chunk)
+                    st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, np.zeros((m, k), vt), k, sop=sop)
+                    assert st == 0 and api.call_info().hub_rows >= 1, (hex(msg), k, d, warps, chunk)
+                    assert rel_err(z, want) <= RTOL[np.dtype(vt)], (hex(msg), k, d, warps, chunk)
+                    if chunk == 256:
+                        assert rel_err(z, z_ref) <= RTOL[np.dtype(vt)] * 0.1
+                api.set_option("hub_chunk", 256)
+    finally:
+        api.set_option("bulk_chunks", 0)
+        api.set_option("bulk_warps", 8)
+        api.set_option("hub_chunk", 256)
+
+
 def test_async_stream_entry(cuda_device, oracle):
     import torch
     rng = np.random.default_rng(10)
