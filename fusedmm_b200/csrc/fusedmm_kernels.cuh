@@ -760,12 +760,25 @@ fused_any_kernel(const Params<T> p)
       auto edge_scalar = [&](long long j, const T *yr) -> T {
          T s;
          if (rop != ROP_NOOP) {
-            s = T(0);
-            for (long long t = lane; t < p.k; t += 32) {
+            // four independent partial sums: four loads of X and of Y in flight per lane instead of one
+            T s4[4] = {T(0), T(0), T(0), T(0)};
+            long long t = lane;
+            for (; t + 96 < p.k; t += 128) {
+               T xe[4], ye[4];
+#pragma unroll
+               for (int q = 0; q < 4; q++) {
+                  xe[q] = need_x ? xr[t + 32 * q] : T(0);
+                  ye[q] = need_y ? __ldg(yr + t + 32 * q) : T(0);
+               }
+#pragma unroll
+               for (int q = 0; q < 4; q++) s4[q] += rop_term(rop, xe[q], vop_apply(vop, xe[q], ye[q]));
+            }
+            for (; t < p.k; t += 32) {
                const T xe = need_x ? xr[t] : T(0);
                const T ye = need_y ? __ldg(yr + t) : T(0);
-               s += rop_term(rop, xe, vop_apply(vop, xe, ye));
+               s4[0] += rop_term(rop, xe, vop_apply(vop, xe, ye));
             }
+            s = (s4[0] + s4[1]) + (s4[2] + s4[3]);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(FULL, s, off);
          } else {

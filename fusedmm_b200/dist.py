@@ -75,6 +75,9 @@ class PeerZ:
         self.multicast = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.row_bytes = k * self.z.element_size()
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self._torch = torch
+        self._side = torch.cuda.Stream(device=device)  # the local fill of rows without edges runs beside the kernels
+        self._fill_pending = False
 
     def peers_at_row(self, r0):
         """Addresses of row ``r0`` in the other ranks' copies of Z."""
@@ -94,18 +97,27 @@ class PeerZ:
     def zero_foreign_empty_rows(self, rowptr, r0, r1, stream=None):
         """The fused exchange does not send rows without edges (a quarter to half of the rows of an R-MAT graph):
         with beta == 0 every rank zeroes those rows of the OTHER ranks' shards in its own copy of Z, from the row
-        pointers it holds anyway.  ``rowptr``: device tensor of n+1 entries; [r0, r1) is this rank's shard."""
+        pointers it holds anyway.  ``rowptr``: device tensor of n+1 entries; [r0, r1) is this rank's shard.
+        The fill is pure store bandwidth on rows nobody else writes in this step, so it is enqueued on a side stream
+        (after the work already on torch's current stream) and runs beside the step's kernels; ``finish_step`` joins
+        it.  ``stream`` is ignored (kept for callers that passed the current stream's handle)."""
         n, k = self.z.shape
+        torch = self._torch
+        self._side.wait_stream(torch.cuda.current_stream())
         st = 0
         if r0 > 0:
-            st = st or api.zero_empty_rows(rowptr[:r0], rowptr[1:r0 + 1], self.z, k, k, stream=stream)
+            st = st or api.zero_empty_rows(rowptr[:r0], rowptr[1:r0 + 1], self.z, k, k, stream=self._side.cuda_stream)
         if r1 < n:
-            st = st or api.zero_empty_rows(rowptr[r1:n], rowptr[r1 + 1:n + 1], self.z[r1:], k, k, stream=stream)
+            st = st or api.zero_empty_rows(rowptr[r1:n], rowptr[r1 + 1:n + 1], self.z[r1:], k, k, stream=self._side.cuda_stream)
+        self._fill_pending = True
         return st
 
     def finish_step(self):
         """Enqueue the collective that follows this rank's kernels in stream order; when it completes on a
         rank, every rank's kernels of the step (and with them their stores into this rank's Z) are done."""
+        if self._fill_pending:
+            self._torch.cuda.current_stream().wait_stream(self._side)
+            self._fill_pending = False
         self.dist.all_reduce(self._token, group=self.group)
 
 
