@@ -75,6 +75,9 @@ struct Params {
    long long *hub_row, *hub_base;
    long long hub_cap, chunk_cap;
    T *partials;                  // chunk_cap x k
+   // optional visiting order of the chunks (order[i] = chunk the i-th work item works on; null: i itself): chunks
+   // sorted by the column id of their first edge, so that the chunks in flight at one time gather from one band of Y
+   const long long *order;
    // edge-stream scheduler (fusedmm_stream.cuh): the edges are cut into quanta of `quantum` edges
    long long quantum;            // edges per work item (a multiple of 32)
    int depth;                    // neighbour rows in flight per virtual warp (power of two <= lanes per edge)
@@ -676,7 +679,7 @@ fused_vec_kernel(const Params<T> p)
          if (w.ee - w.eb > p.chunk) return;
       } else {
          if (wid >= nchunks) return;
-         chunk_item(p, wid, nh, w);
+         chunk_item(p, p.order ? __ldg(p.order + wid) : wid, nh, w);
       }
       T acc[NV][W];
       Eng::template run<false>(p, w, lane, acc);
@@ -748,7 +751,7 @@ fused_any_kernel(const Params<T> p)
          if (w.ee - w.eb > p.chunk) return;
       } else {
          if (wid >= nchunks) return;
-         chunk_item(p, wid, nh, w);
+         chunk_item(p, p.order ? __ldg(p.order + wid) : wid, nh, w);
       }
       const T *xr = p.x + w.row * p.ldx;  // dereferenced only when a stage reads X
       const bool to_z = w.dst_item < 0;
@@ -853,25 +856,101 @@ __global__ void scan_hub_rows(const void *pntrb, const void *pntre, int ptr64, l
                               long long chunk, unsigned long long *counter, long long *hub_row,
                               long long *hub_base, long long hub_cap);
 
-// Pass 3: for every split row, Z_row = AOP(old Z_row or identity, partial_0, partial_1, ...) in chunk
-// order.  One warp per split row, lanes strided over K.
+// Pass 3: for every split row, Z_row = AOP(old Z_row or identity, partial_0, partial_1, ...).
+// Rows of up to FIXUP_LONG chunks: one warp per row, lanes strided over K, the chunks in order.  Longer rows (a row
+// of 400 000 edges has 1 600 chunks, and a single warp adding them one after the other is the tail of the whole call):
+// one block per row; warp w adds the w-th of blockDim.x/32 equal runs of consecutive chunks in order, then warp 0 adds
+// Z_row and the runs' sums in run order.  The association of the additions depends only on the row's chunk count and
+// the block size (fixed), so results are the same from run to run.
+constexpr int FIXUP_LONG = 48;
+
+template <typename T>
+__device__ __forceinline__ void reduce_hub_row_block(const Params<T> &p, long long row, long long base, long long nch,
+                                                     T (*seg)[128])
+{
+   constexpr int EPT = 4;
+   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+   const long long per = (nch + nw - 1) / nw;
+   const long long q0 = warp * per, q1 = q0 + per < nch ? q0 + per : nch;
+   T *zr = p.z + row * p.ldz;
+   for (long long kt = 0; kt < p.k; kt += 32 * EPT) {
+      T a[EPT];
+#pragma unroll
+      for (int e = 0; e < EPT; e++) a[e] = aop_identity<T>(p.aop);
+      const T *src = p.partials + (base + q0) * p.k + kt + lane;
+#pragma unroll 4
+      for (long long q = q0; q < q1; q++, src += p.k) {
+         T v[EPT];
+#pragma unroll
+         for (int e = 0; e < EPT; e++) v[e] = (kt + e * 32 + lane < p.k) ? __ldcg(src + e * 32) : aop_identity<T>(p.aop);
+#pragma unroll
+         for (int e = 0; e < EPT; e++) a[e] = aop_apply(p.aop, a[e], v[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < EPT; e++) seg[warp][e * 32 + lane] = a[e];
+      __syncthreads();
+      if (warp == 0) {
+#pragma unroll
+         for (int e = 0; e < EPT; e++) {
+            const long long t = kt + e * 32 + lane;
+            if (t < p.k) {
+               T r = p.accumulate ? zr[t] : aop_identity<T>(p.aop);
+               for (int w = 0; w < nw && w * per < nch; w++) r = aop_apply(p.aop, r, seg[w][e * 32 + lane]);
+               if (p.z_mc) {
+                  st_multicast(p.z_mc + row * p.ldz + t, r);
+               } else {
+                  zr[t] = r;
+                  for (int g = 0; g < p.n_peers; g++) p.z_peer[g][row * p.ldz + t] = r;
+               }
+            }
+         }
+      }
+      __syncthreads();
+   }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 hub_fixup_kernel(const Params<T> p)
 {
+   __shared__ T seg[WARPS_PER_CTA][128];
+   __shared__ long long long_slot[WARPS_PER_CTA * 32];
+   __shared__ int n_long;
    const int lane = threadIdx.x & 31;
    grid_dependency_wait();  // the partial sums come from the chunk launch that precedes this one
    const unsigned long long c = *p.counter;
    const long long nh = static_cast<long long>(c >> HUB_SHIFT);
    const long long nchunks = static_cast<long long>(c & HUB_CHUNK_MASK);
    if (nh > p.hub_cap || nchunks > p.chunk_cap) return;
+   // the long rows first, so that they do not start last: every thread looks at one slot, the block then works through
+   // the long ones it found.  Neighbouring slots (the longest rows of a skewed graph sit together) go to different blocks.
+   for (long long s0 = 0; s0 < nh; s0 += static_cast<long long>(gridDim.x) * blockDim.x) {
+      if (threadIdx.x == 0) n_long = 0;
+      __syncthreads();
+      const long long slot = s0 + static_cast<long long>(threadIdx.x) * gridDim.x + blockIdx.x;
+      if (slot < nh) {
+         const long long row = p.hub_row[slot];
+         const long long deg = ld_index(p.pntre, row, p.ptr64) - ld_index(p.pntrb, row, p.ptr64);
+         if ((deg + p.chunk - 1) / p.chunk > FIXUP_LONG) long_slot[atomicAdd(&n_long, 1)] = slot;
+      }
+      __syncthreads();
+      const int n = n_long;
+      for (int i = 0; i < n; i++) {
+         const long long sl = long_slot[i];
+         const long long row = p.hub_row[sl], base = p.hub_base[sl];
+         const long long deg = ld_index(p.pntre, row, p.ptr64) - ld_index(p.pntrb, row, p.ptr64);
+         reduce_hub_row_block(p, row, base, (deg + p.chunk - 1) / p.chunk, seg);
+      }
+      __syncthreads();
+   }
    const int wpc = blockDim.x >> 5;
    const long long stride = static_cast<long long>(gridDim.x) * wpc;
    for (long long slot = static_cast<long long>(blockIdx.x) * wpc + (threadIdx.x >> 5); slot < nh;
         slot += stride) {
       const long long row = p.hub_row[slot], base = p.hub_base[slot];
       const long long deg = ld_index(p.pntre, row, p.ptr64) - ld_index(p.pntrb, row, p.ptr64);
-      reduce_hub_row(p, row, base, (deg + p.chunk - 1) / p.chunk, lane);
+      const long long nch = (deg + p.chunk - 1) / p.chunk;
+      if (nch <= FIXUP_LONG) reduce_hub_row(p, row, base, nch, lane);
    }
 }
 

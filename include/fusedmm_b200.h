@@ -355,6 +355,11 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    (default 256; a call whose nnz argument is below 2^24 uses at most 128, below 2^21
  *                    at most 64, unless a row of k values exceeds 1024 bytes).
  *   "chunk_ctas_per_sm"  blocks per SM of the launch that works on the pieces of split rows (default 3).
+ *   "chunk_order"        the pieces of split rows are visited sorted by the column id of their first edge (a counting
+ *                        sort on the device: three more launches per call, none with a plan, which sorts once), so that
+ *                        the pieces in flight at one time gather from one band of Y: 0 never, 1 (default) for graphs of
+ *                        16 M edges and more (judged by the nnz argument, or 16 x m when that is 0), 2 always.  Results
+ *                        do not depend on it.
  *   "force_tiling"   0 = automatic; otherwise (register_budget << 24) | (gathers_in_flight << 16) |
  *                    (lanes_per_edge << 8) | vectors_per_lane; gathers_in_flight 0 means that tiling's
  *                    default, register_budget 0 the compiler's choice (only instantiated combinations

@@ -668,6 +668,57 @@ def test_chunk_launch_through_bulk_copies(cuda_device, oracle, vt):
         api.set_option("hub_chunk", 256)
 
 
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_chunks_visited_in_the_order_of_their_first_column(cuda_device, oracle, vt):
+    """Option chunk_order (on by itself for graphs of 16 M edges and more, forced here): the chunks of split rows are
+    visited sorted by the column id of their first edge (a counting sort on the device) instead of row by row.  Every
+    chunk still writes its own partial sum and the fix-up adds them in the same order, so the result is the unsorted
+    path's bit for bit; device arrays, host arrays and a plan (which sorts once, when it is made); vector and
+    element-strided engine."""
+    import torch
+    rng = np.random.default_rng(78)
+    m, n = 1500, 1300
+    try:
+        for k in (128, 37):
+            pntrb, pntre, indx, val = random_csr(rng, m, n, 5, np.int64, np.int32, hub=2300)
+            val = val.astype(vt)
+            x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+            for msg, sop, chunk in ((M.MSG_SIGMOID, M.SOP_SIGMOID, 64), (M.MSG_TDIST, M.SOP_FR, 256), (M.MSG_SPMM, 0, 32)):
+                api.set_option("hub_chunk", chunk)
+                want = np.zeros((m, k), vt)
+                assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop) == 0
+                api.set_option("chunk_order", 0)
+                for _ in range(2):  # the second call finds the scratch large enough: its launch count is the plain one
+                    st0, z_ref = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, np.zeros((m, k), vt), k, sop=sop)
+                n0 = api.call_info().kernel_launches
+                api.set_option("chunk_order", 2)
+                st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, np.zeros((m, k), vt), k, sop=sop)
+                assert st0 == 0 and st == 0 and api.call_info().hub_rows >= 1
+                assert api.call_info().kernel_launches == n0 + 3, (api.call_info().kernel_launches, n0)
+                assert np.array_equal(z, z_ref), (hex(msg), k, chunk)
+                assert rel_err(z, want) <= RTOL[np.dtype(vt)]
+                zh = np.zeros((m, k), vt)
+                assert api.fusedMM_csr(msg, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, k, y, k, 0.0, zh, k, sop=sop) == 0
+                assert np.array_equal(zh, z_ref), (hex(msg), k, chunk)
+            api.set_option("hub_chunk", 256)
+            for order in (0, 2):
+                api.set_option("chunk_order", order)
+                plan = api.Plan(indx, pntrb, pntre, val)
+                zp = np.zeros((m, k), vt)
+                assert plan.csr(M.MSG_SIGMOID, n, k, x, k, y, k, 0.0, zp, k, sop=M.SOP_SIGMOID) == 0
+                assert api.call_info().hub_rows >= 1
+                plan.close()
+                if order == 0:
+                    zp0 = zp
+            assert np.array_equal(zp, zp0), k
+            want = np.zeros((m, k), vt)
+            assert oracle.csr(M.MSG_SIGMOID, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=M.SOP_SIGMOID) == 0
+            assert rel_err(zp, want) <= RTOL[np.dtype(vt)]
+    finally:
+        api.set_option("chunk_order", 1)
+        api.set_option("hub_chunk", 256)
+
+
 def test_async_stream_entry(cuda_device, oracle):
     import torch
     rng = np.random.default_rng(10)
