@@ -31,6 +31,7 @@ struct fusedmm_b200_plan {
    const void *val = nullptr, *indx = nullptr, *pntrb = nullptr, *pntre = nullptr;  // device addresses used by the calls
    long long *hub_row = nullptr, *hub_base = nullptr;
    long long *order = nullptr;             // visiting order of the chunks (sorted by first column id), or null
+   unsigned int *row_order = nullptr;      // whole rows sorted by length inside windows, or null
    unsigned long long *counter = nullptr;  // packed (split rows << HUB_SHIFT) | chunks, written once by the scan
    long long nh = 0, nchunks = 0;
 };
@@ -149,6 +150,56 @@ __global__ void scan_hub_rows(const void *pntrb, const void *pntre, int ptr64, l
          hub_base[slot] = static_cast<long long>(old & HUB_CHUNK_MASK);
       }
    }
+}
+
+// ---- order of the whole rows (option row_bins) --------------------------------------------------------
+// The whole-row launch gives every group of G lanes of a warp its own row and the 32/G rows of a warp run in
+// lockstep, so a warp takes as long as its longest row.  On a skewed graph neighbouring rows differ widely (R-MAT
+// scale 20: 58 % of the slot-iterations do work; with rows of equal length side by side, 91 %).  This kernel sorts
+// the rows of every window of ROW_BIN_TILE consecutive rows by their number of edges, longest first (a counting sort
+// in shared memory), and writes the permutation; rows without edges and split rows (which the whole-row launch
+// skips) come last.  Rows stay inside their window, so X, Z and the row pointers are still read window by window.
+constexpr int ROW_BIN_TILE = 2048, ROW_BIN_KEYS = 258;
+
+__global__ void __launch_bounds__(256)
+bin_rows_kernel(const void *pntrb, const void *pntre, int ptr64, long long m, long long chunk, unsigned int *row_order)
+{
+   __shared__ unsigned int hist[ROW_BIN_KEYS];
+   constexpr int PER = ROW_BIN_TILE / 256;
+   const long long base = static_cast<long long>(blockIdx.x) * ROW_BIN_TILE;
+   for (int b = threadIdx.x; b < ROW_BIN_KEYS; b += 256) hist[b] = 0;
+   __syncthreads();
+   int key[PER];
+#pragma unroll
+   for (int i = 0; i < PER; i++) {
+      const long long r = base + i * 256 + threadIdx.x;
+      key[i] = -1;
+      if (r < m) {
+         const long long deg = ld_index(pntre, r, ptr64) - ld_index(pntrb, r, ptr64);
+         // bin 0: the longest whole rows ... bin 256: one edge; bin 257: nothing to do in the whole-row launch
+         key[i] = (deg <= 0 || deg > chunk) ? ROW_BIN_KEYS - 1 : (deg >= 256 ? 0 : 256 - static_cast<int>(deg));
+         atomicAdd(hist + key[i], 1u);
+      }
+   }
+   __syncthreads();
+   if (threadIdx.x < 32) {  // exclusive prefix sums of the 258 counters by one warp
+      unsigned int run = 0;
+      for (int b0 = 0; b0 < ROW_BIN_KEYS; b0 += 32) {
+         const int b = b0 + threadIdx.x;
+         const unsigned int v = b < ROW_BIN_KEYS ? hist[b] : 0u;
+         unsigned int inc = v;
+         for (int off = 1; off < 32; off <<= 1) {
+            const unsigned int up = __shfl_up_sync(FULL, inc, off);
+            if (static_cast<int>(threadIdx.x) >= off) inc += up;
+         }
+         if (b < ROW_BIN_KEYS) hist[b] = run + inc - v;
+         run += __shfl_sync(FULL, inc, 31);
+      }
+   }
+   __syncthreads();
+#pragma unroll
+   for (int i = 0; i < PER; i++)
+      if (key[i] >= 0) row_order[base + atomicAdd(hist + key[i], 1u)] = static_cast<unsigned int>(base + i * 256 + threadIdx.x);
 }
 
 // ---- visiting order of the chunks of split rows (option chunk_order) ---------------------------------
@@ -316,6 +367,7 @@ struct DeviceCtx {
    int sm_count = 148;
    DevBuf stage[7];  // val, indx, pntrb, pntre, x, y, z
    DevBuf counter, hub_row, hub_base, partials;
+   DevBuf row_order;  // option row_bins: permutation of the rows for the whole-row launch
    DevBuf order, order_cnt;  // option chunk_order: visiting order of the chunks; 3 x ORDER_BUCKETS counters
    long long hub_cap = 0;
    DevBuf part, heads;       // edge-stream scheduler scratch
@@ -331,8 +383,8 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
-           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, chunk_order = 1, side_stream = 1, force_tiling_rows = 0,
-           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, exact_k = 1, element_vectors = 1, bulk_chunks = 0, bulk_warps = 8, bulk_ctas_per_sm = 0, hub_cap_initial = 1 << 16;
+           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, chunk_order = 1, row_bins = 1, side_stream = 1, force_tiling_rows = 0,
+           strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, offset32 = 1, exact_k = 1, element_vectors = 1, bulk_chunks = 0, bulk_warps = 8, bulk_ctas_per_sm = 0, hub_cap_initial = 1 << 16;
 };
 
 // Locking: g_mu guards the process-wide settings (options, default SOP) and the creation of device contexts; each
@@ -896,7 +948,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    int jit_flags = element_mode ? FLAG_ELEMENT : 0;
    if (vec_ok && !element_mode && t_opt.jit_call_shape && t_opt.jit > 0 && !t_opt.force_generic && (jit_weight >= (1ll << 26) || t_opt.jit_call_shape == 2)) {
       const bool need_y_ = vop_reads_y(d.vop);
-      if (need_y_ && a.idx_bits == 32 && a.n > 0 && static_cast<double>(a.n - 1) * static_cast<double>(a.ldy) + static_cast<double>(a.k) <= 4294967295.0)
+      if (need_y_ && a.idx_bits == 32 && static_cast<double>(a.ldy) * es < 4294967296.0)
          jit_flags |= FLAG_OFFSET32;
       jit_flags &= static_cast<int>(t_opt.jit_shape_mask);
       if (jit_flags & FLAG_OFFSET32) jit_policy = std::max<int>(jit_policy, static_cast<int>(t_opt.jit));
@@ -910,6 +962,14 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
                                               jit_weight)) {
          jit_used = true;
          return true;
+      }
+      if (t_opt.offset32 && need_y && !element_mode && a.idx_bits == 32 && static_cast<double>(a.ldy) * es < 4294967296.0 &&
+          q.mode == MODE_ROWS) {
+         // 32-bit column ids: the variant with the one-instruction row address, for the tiling that has one (fusedmm_inst.cuh)
+         const int u_budget = (u_rt & 0xFF) | (jit_budget(g, nv, u_rt & 0xFF, (u_rt >> 8) & 0xFF) << 8);
+         if (ex && launch_vec<T>(pattern, g, nv, u_budget | (5 << 16), w, q, grid, s)) return true;
+         if (ex && launch_vec<T>(pattern, g, nv, u_rt | (5 << 16), w, q, grid, s)) return true;
+         if (!ex && launch_vec<T>(pattern, g, nv, u_rt | (4 << 16), w, q, grid, s)) return true;
       }
       if (fl & FLAG_EXACT_K) {
          // without the predicates the offline compiler no longer settles on 80 registers for (32, 2, 4) by itself (93):
@@ -1029,6 +1089,11 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // floats 28.4 -> 24.3 ms, 520 M edges with K = 128 41.8 -> 40.0 ms, 31 M edges with K = 256 3.96 -> 3.91 ms,
    // 0.4 M edges 59 -> 87 us.
    const long long est_edges = a.nnz > 0 ? a.nnz : a.m * 16;
+   // Whole rows sorted by length inside windows (option row_bins: 0 never, 1 for graphs of 4 M edges and more, 2
+   // always): only where several rows share a warp (fewer than 32 lanes per edge), and never for a call that could
+   // not name its rows in 32 bits.
+   bool use_bins = !a.plan && vec_ok && Gr < 32 && a.m < (1ll << 32) &&
+                   (t_opt.row_bins == 2 || (t_opt.row_bins == 1 && est_edges >= (1ll << 22)));
    bool use_order = !a.plan && need_y && (t_opt.chunk_order == 2 || (t_opt.chunk_order == 1 && est_edges >= (1ll << 24)));
 
    // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
@@ -1085,6 +1150,13 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       launches += 2;
       if (with_rows) {  // whole rows only once: a rerun after a scratch overflow redoes split rows only
          q.mode = MODE_ROWS;
+         if (!a.plan) q.row_order = nullptr;
+         if (use_bins && q.m > 0) {
+            bin_rows_kernel<<<static_cast<unsigned int>((q.m + ROW_BIN_TILE - 1) / ROW_BIN_TILE), 256, 0, st>>>(
+               q.pntrb, q.pntre, q.ptr64, q.m, q.chunk, static_cast<unsigned int *>(c.row_order.ptr));
+            q.row_order = static_cast<const unsigned int *>(c.row_order.ptr);
+            launches++;
+         }
          if (vec_ok) { if (!launch_main(q, Gr, NVr, Ur, Urs, warps, qgrid, st)) return FUSEDMM_B200_ERR_ARG; }
          else launch_any<T>(q, warps, qgrid, st);
          launches++;
@@ -1102,6 +1174,8 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       if (a.plan) q.order = (need_y && t_opt.chunk_order != 0) ? a.plan->order : nullptr;
       q.partials = static_cast<T *>(c.partials.ptr);
       q.chunk_cap = static_cast<long long>(c.partials.bytes / (static_cast<size_t>(a.k) * es));
+      if (use_bins && ensure_buf(c.row_order, static_cast<size_t>(a.m) * sizeof(unsigned int))) use_bins = false;
+      if (a.plan) q.row_order = (vec_ok && Gr < 32 && t_opt.row_bins != 0) ? a.plan->row_order : nullptr;
       if (use_order) {
          if (ensure_buf(c.order, static_cast<size_t>(q.chunk_cap) * sizeof(long long))) use_order = false;
          if (ensure_buf(c.order_cnt, 3 * ORDER_BUCKETS * sizeof(unsigned int))) use_order = false;
@@ -1798,6 +1872,12 @@ int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int6
           cudaStreamSynchronize(c->stream) != cudaSuccess) return fail(FUSEDMM_B200_ERR_CUDA);
       pl->nh = static_cast<long long>(packed >> HUB_SHIFT);
       pl->nchunks = static_cast<long long>(packed & HUB_CHUNK_MASK);
+      if (t_opt.row_bins != 0 && m < (1ll << 32) && (t_opt.row_bins == 2 || ext >= (1ll << 22))) {
+         if (cudaMalloc(&pl->row_order, m * sizeof(unsigned int)) != cudaSuccess) { cudaGetLastError(); return fail(FUSEDMM_B200_ERR_NOMEM); }
+         bin_rows_kernel<<<static_cast<unsigned int>((m + ROW_BIN_TILE - 1) / ROW_BIN_TILE), 256, 0, c->stream>>>(
+            pl->pntrb, pl->pntre, ptr_bits == 64, m, pl->chunk, pl->row_order);
+         if (cudaStreamSynchronize(c->stream) != cudaSuccess) return fail(FUSEDMM_B200_ERR_CUDA);
+      }
       // the visiting order of the chunks is made once here; the column count is not an argument of a plan: the largest
       // first column id of a chunk stands in for it
       if (pl->indx && ((t_opt.chunk_order == 1 && pl->nchunks >= 1024) || (t_opt.chunk_order == 2 && pl->nchunks > 0))) {
@@ -1847,6 +1927,7 @@ int fusedmm_b200_plan_destroy(fusedmm_b200_plan *plan)
    if (plan->hub_row) cudaFree(plan->hub_row);
    if (plan->hub_base) cudaFree(plan->hub_base);
    if (plan->order) cudaFree(plan->order);
+   if (plan->row_order) cudaFree(plan->row_order);
    if (plan->counter) cudaFree(plan->counter);
    delete plan;
    return 0;
@@ -1979,11 +2060,13 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "force_tiling_rows")) return &g_opt.force_tiling_rows;
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "chunk_order")) return &g_opt.chunk_order;
+   if (!strcmp(name, "row_bins")) return &g_opt.row_bins;
    if (!strcmp(name, "strict_udef")) return &g_opt.strict_udef;
    if (!strcmp(name, "multi_skip_empty_rows")) return &g_opt.multi_skip_empty_rows;
    if (!strcmp(name, "jit")) return &g_opt.jit;
    if (!strcmp(name, "pdl")) return &g_opt.pdl;
    if (!strcmp(name, "jit_call_shape")) return &g_opt.jit_call_shape;
+   if (!strcmp(name, "offset32")) return &g_opt.offset32;
    if (!strcmp(name, "hub_cap_initial")) return &g_opt.hub_cap_initial;
    if (!strcmp(name, "jit_shape_mask")) return &g_opt.jit_shape_mask;
    if (!strcmp(name, "exact_k")) return &g_opt.exact_k;
@@ -2033,7 +2116,7 @@ int fusedmm_b200_set_option(const char *name, int64_t value)
    if (s == &g_opt.warps_per_cta && (value < 1 || value > WARPS_PER_CTA)) return FUSEDMM_B200_ERR_ARG;
    if ((s == &g_opt.engine || s == &g_opt.jit || s == &g_opt.jit_call_shape) && value > 2) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.chunk_ctas_per_sm && (value < 1 || value > 64)) return FUSEDMM_B200_ERR_ARG;
-   if (s == &g_opt.chunk_order && (value < 0 || value > 2)) return FUSEDMM_B200_ERR_ARG;
+   if ((s == &g_opt.chunk_order || s == &g_opt.row_bins) && (value < 0 || value > 2)) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.edge_quantum && (value < 32 || value > (1ll << 24))) return FUSEDMM_B200_ERR_ARG;
    if (s == &g_opt.stream_depth && (value < 1 || value > 32)) return FUSEDMM_B200_ERR_ARG;
    *s = value;
@@ -2086,7 +2169,7 @@ int fusedmm_b200_release(void)
       cudaSetDevice(c.device);
       cudaStreamSynchronize(c.stream);
       DevBuf *bufs[] = {&c.stage[0], &c.stage[1], &c.stage[2], &c.stage[3], &c.stage[4], &c.stage[5], &c.stage[6],
-                        &c.hub_row, &c.hub_base, &c.partials, &c.order, &c.order_cnt, &c.table_f, &c.table_d, &c.part, &c.heads};
+                        &c.hub_row, &c.hub_base, &c.partials, &c.order, &c.order_cnt, &c.row_order, &c.table_f, &c.table_d, &c.part, &c.heads};
       for (DevBuf *b : bufs) { if (b->ptr) cudaFree(b->ptr); b->ptr = nullptr; b->bytes = 0; }
       c.hub_cap = 0;
       c.part_cap = 0;

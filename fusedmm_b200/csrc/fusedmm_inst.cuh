@@ -28,6 +28,14 @@ namespace fmm {
 #define FMM_FOR_EACH_ELEMENT_TILING(X) \
    X(4, 1, 4, 0) X(8, 1, 8, 0) X(8, 2, 4, 4) X(16, 2, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 3) X(32, 8, 1, 0) X(32, 16, 1, 0)
 
+// 32-bit column ids (FLAG_OFFSET32: the address of a neighbour row in one multiply-add), plain and exact-K forms, for
+// the one tiling that gains from it: whole rows of 17 to 32 vectors of 16 bytes (K = 128 floats on R-MAT scale 24: the
+// call 40.4 -> 38.9 ms).  The 32-lane tilings lose with it in both launches although they execute fewer instructions
+// (K = 128 doubles 80.4 -> 83.9 ms in the whole-row launch alone, 93.9 in both; K = 512 floats 23.4 -> 24.6 / 26.1;
+// K = 256 floats 3.94 -> 4.10 / 4.13), and so does the chunk launch of K = 128 floats (24.0 -> 24.3 ms).
+#define FMM_FOR_EACH_OFF32_TILING(X) X(16, 2, 4, 3)
+#define FMM_FOR_EACH_OFF32_EXACT_TILING(X) X(16, 2, 4, 3)
+
 // A translation unit may add tilings of its own by defining this before the include (the flag-interpreting
 // kernels need other register budgets than the specialised ones).
 #ifndef FMM_FOR_EACH_EXTRA_TILING
@@ -52,6 +60,17 @@ namespace fmm {
    case (1 << 28) | ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                               \
       launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_,             \
                                          FLAG_EXACT_K>, grid, warps * 32, stream, p);                 \
+      return true;
+
+#define FMM_OFF32_TILING_CASE(G_, NV_, U_, MB_)                                                      \
+   case (4 << 28) | ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                               \
+      launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_,             \
+                                         FLAG_OFFSET32>, grid, warps * 32, stream, p);                \
+      return true;
+#define FMM_OFF32_EXACT_TILING_CASE(G_, NV_, U_, MB_)                                                \
+   case (5 << 28) | ((MB_) << 24) | ((U_) << 16) | ((G_) << 8) | (NV_):                               \
+      launch_kernel<T_>(fused_vec_kernel<T_, VOPC_, ROPC_, VSCC_, AOPC_, G_, NV_, U_, MB_,             \
+                                         FLAG_OFFSET32 | FLAG_EXACT_K>, grid, warps * 32, stream, p); \
       return true;
 
 // persistent launch of the edge-stream kernel: as many CTAs as fit on the device at once
@@ -113,14 +132,16 @@ namespace fmm {
       using T_ = T;                                                                                   \
       constexpr int VOPC_ = VOPC, ROPC_ = ROPC, VSCC_ = VSCC, AOPC_ = AOPC;                           \
       /* U carries the register budget class MB in bits 8..15 (0 = compiler's choice) and the call-shape   */ \
-      /* flags in bits 16..: 1 = FLAG_EXACT_K, 2 = FLAG_ELEMENT (never both here)                         */ \
-      const int MB = (U >> 8) & 0xFF, FL = (U >> 16) & 3;                                             \
+      /* flags in bits 16..: 1 = FLAG_EXACT_K, 2 = FLAG_ELEMENT (never both here), 4 = FLAG_OFFSET32       */ \
+      const int MB = (U >> 8) & 0xFF, FL = (U >> 16) & 7;                                             \
       U &= 0xFF;                                                                                      \
       switch ((FL << 28) | (MB << 24) | (U << 16) | (G << 8) | NV) {                                  \
          FMM_FOR_EACH_TILING(FMM_TILING_CASE)                                                         \
          FMM_FOR_EACH_EXTRA_TILING(FMM_TILING_CASE)                                                   \
          FMM_FOR_EACH_EXACT_TILING(FMM_EXACT_TILING_CASE)                                             \
          FMM_FOR_EACH_ELEMENT_TILING(FMM_ELEMENT_TILING_CASE)                                         \
+         FMM_FOR_EACH_OFF32_TILING(FMM_OFF32_TILING_CASE)                                             \
+         FMM_FOR_EACH_OFF32_EXACT_TILING(FMM_OFF32_EXACT_TILING_CASE)                                 \
          default: return false;                                                                       \
       }                                                                                               \
    }

@@ -78,6 +78,10 @@ struct Params {
    // optional visiting order of the chunks (order[i] = chunk the i-th work item works on; null: i itself): chunks
    // sorted by the column id of their first edge, so that the chunks in flight at one time gather from one band of Y
    const long long *order;
+   // optional order of the whole rows (row_order[i] = row of the i-th slot of the whole-row launch; null: i itself):
+   // rows sorted by their number of edges inside windows of consecutive rows, so that the rows that share a warp
+   // (32/G of them, in lockstep) are about equally long
+   const unsigned int *row_order;
    // edge-stream scheduler (fusedmm_stream.cuh): the edges are cut into quanta of `quantum` edges
    long long quantum;            // edges per work item (a multiple of 32)
    int depth;                    // neighbour rows in flight per virtual warp (power of two <= lanes per edge)
@@ -429,8 +433,9 @@ __device__ __forceinline__ void reduce_hub_row(const Params<T> &p, long long row
 // FLAGS: properties of the CALL (not of the message) that a kernel built at run time for that call may assume:
 //   FLAG_EXACT_K   k == G*NV*W: no vector of the tiling lies beyond the end of a row, so the per-vector bounds
 //                  predicates on every gather and store go away;
-//   FLAG_OFFSET32  column ids are 32 bits wide and every element offset into Y (cid*ldy + k) is below 2^32: the row
-//                  offset is one 32x32->64-bit multiply-add instead of a 64-bit multiply per edge.
+//   FLAG_OFFSET32  column ids are 32 bits wide (and not negative) and a row of Y is less than 2^32 bytes from the next:
+//                  the address of a lane's piece of a neighbour row is ONE 32 x 32 + 64-bit multiply-add on the lane's
+//                  own base address, instead of a 64-bit multiply, a scaled add and one 64-bit add per vector.
 //   FLAG_ELEMENT   vectors of ONE element instead of 16 bytes: for calls whose K, leading dimensions or base addresses
 //                  are not multiples of 16 bytes (K up to G*NV elements).
 // FLAGS = 0 takes every call whose rows are 16-byte granular.
@@ -488,12 +493,18 @@ struct VecEngine {
 #pragma unroll
             for (int i = 0; i < W; i++) yv[u][v][i] = T(0);
       const int u_mine = lg / (G / U);  // the edge of a group whose scalar this lane ends up holding
+      // FLAG_OFFSET32: byte address of this lane's first vector in row 0 of Y, and the row pitch in bytes (< 2^32)
+      const char *y_lane = reinterpret_cast<const char *>(p.y + lg * W);
+      const unsigned int ldy_bytes = static_cast<unsigned int>(p.ldy * static_cast<long long>(sizeof(T)));
       const int eslot = MULTI ? 0 : slot;
       const int blane = MULTI ? lg : lane;
 
       for (long long base = w.eb; MULTI ? __any_sync(FULL, base < w.ee) : (base < w.ee); base += BW) {
          const long long j = base + blane;
-         const long long my_cid = (j < w.ee && need_y) ? ld_index(p.indx, j, p.idx64) : 0;
+         long long my_cid = 0;
+         unsigned int my_cid32 = 0;  // FLAG_OFFSET32: column ids are 32 bits wide
+         if constexpr (OFFSET32) { if (j < w.ee && need_y) my_cid32 = static_cast<unsigned int>(__ldg(static_cast<const int *>(p.indx) + j)); }
+         else { if (j < w.ee && need_y) my_cid = ld_index(p.indx, j, p.idx64); }
          const T my_val = (use_val && j < w.ee) ? __ldg(p.val + j) : T(0);
          const long long left = w.ee - base;
          const int nb = left < BW ? (left > 0 ? static_cast<int>(left) : 0) : BW;
@@ -507,8 +518,9 @@ struct VecEngine {
                ok[u] = e < nb;
                const T *yrow;
                if constexpr (OFFSET32) {
-                  const unsigned int cid = static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW));
-                  yrow = p.y + static_cast<unsigned long long>(cid * static_cast<unsigned int>(p.ldy));
+                  // one 32 x 32 + 64-bit multiply-add: the lane's byte address in the neighbour's row
+                  const unsigned int cid = __shfl_sync(FULL, my_cid32, e, BW);
+                  yrow = reinterpret_cast<const T *>(y_lane + static_cast<unsigned long long>(cid) * ldy_bytes);
                } else {
                   const long long cid = p.idx64 ? (static_cast<long long>(__shfl_sync(FULL, static_cast<int>(my_cid >> 32), e, BW)) << 32) |
                                                      static_cast<unsigned int>(__shfl_sync(FULL, static_cast<int>(my_cid), e, BW))
@@ -517,7 +529,7 @@ struct VecEngine {
                }
 #pragma unroll
                for (int v = 0; v < NV; v++)
-                  if (need_y && ok[u] && inb[v]) ld_vec_nc(yrow + static_cast<long long>(v * G + lg) * W, yv[u][v]);
+                  if (need_y && ok[u] && inb[v]) ld_vec_nc(yrow + (OFFSET32 ? v * G * W : static_cast<long long>(v * G + lg) * W), yv[u][v]);
             }
             // ---- pass 1: T = VOP(x, y) in place, and this lane's share of each edge's reduction ----
             T part[U];
@@ -634,6 +646,7 @@ fused_vec_kernel(const Params<T> p)
       w.dst_item = -1;
       w.eb = w.ee = 0;
       bool mine = w.row < p.m;
+      if (mine && p.row_order) w.row = __ldg(p.row_order + w.row);
       if (mine) {
          w.eb = ld_index(p.pntrb, w.row, p.ptr64);
          w.ee = ld_index(p.pntre, w.row, p.ptr64);

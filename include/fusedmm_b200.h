@@ -415,10 +415,14 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    (fusedmm_b200/csrc/fusedmm_bulk.cuh; the four optimised messages only).  Same results; measured
  *                    15 % to 2.4x slower on the benchmark configurations.  "bulk_warps" (1..8, default 8): warps per
  *                    block of that launch; "bulk_ctas_per_sm" (0 = as many as fit).
- *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time that
- *                    also uses 32-bit row offsets when column ids are 32 bits wide and Y lies within 2^32 elements;
- *                    2: every call does.  Bit-identical results; measured 4-50 % slower: an experiment, left off.
- *   "jit_shape_mask" bit 1 switches the 32-bit row offsets of "jit_call_shape" on (default 3).
+ *   "offset32"       1 (default): with 32-bit column ids and rows of Y less than 2^32 bytes apart, the whole-row launch
+ *                    of calls with 68..128 floats (34..64 doubles) per row runs the instantiation that forms a neighbour
+ *                    row's address with one 32 x 32 + 64-bit multiply-add (bit-identical results; 4 % faster at
+ *                    k = 128 floats; the other tilings measured slower with it and have no such form); 0: never.
+ *   "jit_call_shape" 0 (default); 1: a call with nnz * k >= 2^26 of ANY message runs a kernel built at run time for
+ *                    the shape of the call (exact k, 32-bit column ids) in BOTH launches; 2: every call does.
+ *                    Bit-identical results; an experiment, left off.
+ *   "jit_shape_mask" bit 1 switches the 32-bit column ids of "jit_call_shape" on (default 3).
  *   "hub_cap_initial"  split rows the hub list has room for when it is first allocated (default 65536; it grows on
  *                    demand, this only sets where the growth starts: tests use it to reach the growth path).
  *   "inject_alloc_failure"  n > 0: the n-th device allocation the library attempts from now on fails

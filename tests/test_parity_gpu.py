@@ -719,6 +719,86 @@ def test_chunks_visited_in_the_order_of_their_first_column(cuda_device, oracle, 
         api.set_option("hub_chunk", 256)
 
 
+def test_one_multiply_add_row_addresses_with_32_bit_column_ids(cuda_device, oracle):
+    """Option offset32 (on by default): with 32-bit column ids the whole-row launch of the 16-lane tiling forms the
+    address of a neighbour row with one multiply-add.  Same bits as the 64-bit form (option off, or 64-bit column
+    ids), K filling the tiling and ragged, Y more than 2^32 bytes long in total."""
+    import torch
+    rng = np.random.default_rng(79)
+    m = 700
+    try:
+        for vt, k, n in ((np.float32, 128, 900), (np.float32, 100, 900), (np.float64, 64, 900), (np.float64, 50, 900),
+                         (np.float32, 128, (1 << 23) + 4096)):
+            free_b, _ = torch.cuda.mem_get_info()
+            if n * k * np.dtype(vt).itemsize * 3 > free_b:
+                continue
+            pntrb, pntre, indx, val = random_csr(rng, m, n, 9, np.int64, np.int32, hub=600)
+            assert 0 <= indx.min() and indx.max() < n   # with the long Y: neighbours on both sides of byte 2^32
+            val = val.astype(vt)
+            x = np.nan_to_num(dense(rng, m, k, k, vt))
+            y = dev(np.nan_to_num(dense(rng, 900, k, k, vt)), cuda_device).repeat((n + 899) // 900, 1)[:n].contiguous()
+            tx, tv = dev(x, cuda_device), dev(val, cuda_device)
+            tb, te = dev(pntrb, cuda_device), dev(pntre, cuda_device)
+            for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_SPMM, 0)):
+                outs = []
+                for off32, it in ((1, np.int32), (0, np.int32), (1, np.int64)):
+                    api.set_option("offset32", off32)
+                    z = torch.zeros((m, k), dtype=y.dtype, device=cuda_device)
+                    ti = dev(indx.astype(it), cuda_device)
+                    assert api.fusedMM_csr(msg, m, n, k, 1.0, 0, m, n, tv, ti, tb, te, tx, k, y, k, 0.0, z, k, sop=sop) == 0
+                    torch.cuda.synchronize()
+                    assert api.call_info().lanes_per_edge in (16, 32)
+                    outs.append(z.cpu().numpy())
+                assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2]), (vt, k, n, hex(msg))
+                # Y repeats with period 900: the oracle works on the first 900 rows and the column ids modulo 900
+                want = np.zeros((m, k), vt)
+                assert oracle.csr(msg, m, 900, k, val, (indx % 900).astype(np.int32), pntrb, pntre, x, k, y[:900].cpu().numpy(), k, 0.0,
+                                  want, k, sop_kind=sop) == 0
+                assert rel_err(outs[0], want) <= RTOL[np.dtype(vt)]
+            del y
+    finally:
+        api.set_option("offset32", 1)
+
+
+@pytest.mark.parametrize("vt", [np.float32, np.float64])
+def test_whole_rows_sorted_by_length_inside_windows(cuda_device, oracle, vt):
+    """Option row_bins (on by itself for graphs of 4 M edges and more, forced here): the whole-row launch takes its rows
+    from a permutation that sorts every window of 2048 consecutive rows by length, so that the rows sharing a warp are
+    about equally long.  Every row is still computed by one group of lanes over its edges in order: same bits as the
+    unsorted launch; several windows and a ragged last one, 2 / 4 / 8 rows per warp, direct call, host arrays, plan."""
+    rng = np.random.default_rng(80)
+    m, n = 2048 * 3 + 777, 3000
+    w = 4 if vt == np.float32 else 2
+    try:
+        for k in (32 * w, 16 * w - w, 8 * w, 3):
+            pntrb, pntre, indx, val = random_csr(rng, m, n, 7, np.int64, np.int32, hub=700, gaps=True)
+            val = val.astype(vt)
+            x, y = np.nan_to_num(dense(rng, m, k, k, vt)), np.nan_to_num(dense(rng, n, k, k, vt))
+            for msg, sop in ((M.MSG_SIGMOID, M.SOP_SIGMOID), (M.MSG_GCN, 0)):
+                want = np.zeros((m, k), vt)
+                assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, want, k, sop_kind=sop) == 0
+                outs = []
+                for bins in (0, 2):
+                    api.set_option("row_bins", bins)
+                    st, z = run_gpu(cuda_device, msg, m, n, k, val, indx, pntrb, pntre, x, k, y, k, 0.0, np.zeros((m, k), vt), k, sop=sop)
+                    assert st == 0 and api.call_info().lanes_per_edge < 32
+                    launches = api.call_info().kernel_launches
+                    zh = np.zeros((m, k), vt)
+                    assert api.fusedMM_csr(msg, m, n, k, 1.0, 0, m, n, val, indx, pntrb, pntre, x, k, y, k, 0.0, zh, k, sop=sop) == 0
+                    plan = api.Plan(indx, pntrb, pntre, val)
+                    zp = np.zeros((m, k), vt)
+                    assert plan.csr(msg, n, k, x, k, y, k, 0.0, zp, k, sop=sop) == 0
+                    plan.close()
+                    outs.append((z, zh, zp, launches))
+                assert outs[1][3] == outs[0][3] + 1
+                for i in range(3):
+                    assert np.array_equal(outs[0][i], outs[1][i]), (k, hex(msg), i)
+                assert np.array_equal(outs[1][0], outs[1][1])
+                assert rel_err(outs[1][0], want) <= RTOL[np.dtype(vt)]
+    finally:
+        api.set_option("row_bins", 1)
+
+
 def test_async_stream_entry(cuda_device, oracle):
     import torch
     rng = np.random.default_rng(10)
