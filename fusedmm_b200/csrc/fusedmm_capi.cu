@@ -658,8 +658,13 @@ void choose_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
 // (at most `chunk` edges, on R-MAT graphs ten on average), so fewer gathers per slot are outstanding anyway and more
 // resident warps pay more.  K = 128 floats on R-MAT scale 24: 43.7 ms per call with (16, 2, 4) in 80 registers for
 // the whole rows against 45.4 with the chunk launch's (16, 2, 8) in 128.  false: use the chunk launch's tiling.
-bool choose_rows_tiling(long long nvec, bool is_double, int *G, int *NV, int *U)
+// With the whole rows sorted by length (option row_bins) two rows per warp pay for rows of 33..64 vectors as well:
+// (16, 4, 2) in 80 registers, K = 128 doubles on R-MAT scale 24 75.8 ms against 80.5 with (32, 2, 4), K = 256 floats on
+// scale 20 3.77 against 3.91 (without the sorting it loses: 89.8 against 85.9 and 4.70 against 4.29); K = 512 floats
+// stays with one row per warp ((16, 8, 1): 24.4-25.0 ms against 24.4).
+bool choose_rows_tiling(long long nvec, bool is_double, bool binned, int *G, int *NV, int *U)
 {
+   if (binned && nvec > 32 && nvec <= 64) { *G = 16; *NV = 4; *U = 2 | (3 << 8); return true; }
    if (!is_double && nvec > 16 && nvec <= 32) { *G = 16; *NV = 2; *U = 4 | (3 << 8); return true; }
    // K = 128 doubles, same graph: 85.9 ms with (32, 2, 4) in 80 registers for the whole rows against 90.6 with (32, 2, 8)
    if (is_double && nvec > 32 && nvec <= 64) { *G = 32; *NV = 2; *U = 4 | (3 << 8); return true; }
@@ -918,11 +923,18 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       if (Us == 0) Us = U;
       if (G == 0 || static_cast<long long>(G) * NV * W < a.k) vec_ok = false;
    }
+   // Whole rows sorted by length inside windows (option row_bins: 0 never, 1 for graphs of 4 M edges and more, 2
+   // always; a plan has sorted them when it was made), for launches in which several rows share a warp; never for a
+   // call that could not name its rows in 32 bits.
+   const long long est_edges = a.nnz > 0 ? a.nnz : a.m * 16;
+   const bool bins_wanted = vec_ok && a.m < (1ll << 32) &&
+                            (a.plan ? (a.plan->row_order != nullptr && t_opt.row_bins != 0)
+                                    : (t_opt.row_bins == 2 || (t_opt.row_bins == 1 && est_edges >= (1ll << 22))));
    // the whole-row launch may use a tiling of its own (short rows are latency-bound, chunks throughput-bound)
    int Gr = G, NVr = NV, Ur = U, Urs = Us;  // Urs: U | budget of a specialised kernel for the whole rows
    if (vec_ok && !element_mode && !t_opt.force_tiling && !t_opt.force_tiling_rows) {
       int g2 = 0, nv2 = 0, u2 = 0;
-      if (choose_rows_tiling(a.k / W, sizeof(T) == 8, &g2, &nv2, &u2) && static_cast<long long>(g2) * nv2 * W >= a.k) {
+      if (choose_rows_tiling(a.k / W, sizeof(T) == 8, bins_wanted, &g2, &nv2, &u2) && static_cast<long long>(g2) * nv2 * W >= a.k) {
          if (d.pattern != PAT_GENERIC && !t_opt.force_generic) { Gr = g2; NVr = nv2; Ur = u2; Urs = u2; }
          else if (g2 == G && nv2 == NV) Urs = u2;  // the flag-interpreting kernel keeps its own; one built for the message takes it
       }
@@ -1088,12 +1100,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
    // enough for the three launches of the sort to pay, 2 always).  Measured on R-MAT graphs: 16 M edges with K = 512
    // floats 28.4 -> 24.3 ms, 520 M edges with K = 128 41.8 -> 40.0 ms, 31 M edges with K = 256 3.96 -> 3.91 ms,
    // 0.4 M edges 59 -> 87 us.
-   const long long est_edges = a.nnz > 0 ? a.nnz : a.m * 16;
-   // Whole rows sorted by length inside windows (option row_bins: 0 never, 1 for graphs of 4 M edges and more, 2
-   // always): only where several rows share a warp (fewer than 32 lanes per edge), and never for a call that could
-   // not name its rows in 32 bits.
-   bool use_bins = !a.plan && vec_ok && Gr < 32 && a.m < (1ll << 32) &&
-                   (t_opt.row_bins == 2 || (t_opt.row_bins == 1 && est_edges >= (1ll << 22)));
+   bool use_bins = !a.plan && bins_wanted && Gr < 32;
    bool use_order = !a.plan && need_y && (t_opt.chunk_order == 2 || (t_opt.chunk_order == 1 && est_edges >= (1ll << 24)));
 
    // One pass of the row scheduler over the rows that `q` describes: scan, then the chunks of split rows
@@ -1175,7 +1182,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       q.partials = static_cast<T *>(c.partials.ptr);
       q.chunk_cap = static_cast<long long>(c.partials.bytes / (static_cast<size_t>(a.k) * es));
       if (use_bins && ensure_buf(c.row_order, static_cast<size_t>(a.m) * sizeof(unsigned int))) use_bins = false;
-      if (a.plan) q.row_order = (vec_ok && Gr < 32 && t_opt.row_bins != 0) ? a.plan->row_order : nullptr;
+      if (a.plan) q.row_order = (bins_wanted && Gr < 32) ? a.plan->row_order : nullptr;
       if (use_order) {
          if (ensure_buf(c.order, static_cast<size_t>(q.chunk_cap) * sizeof(long long))) use_order = false;
          if (ensure_buf(c.order_cnt, 3 * ORDER_BUCKETS * sizeof(unsigned int))) use_order = false;

@@ -12,7 +12,7 @@ namespace fmm {
 #define FMM_FOR_EACH_TILING(X) \
    X(4, 1, 4, 0) X(8, 1, 8, 0) X(8, 2, 4, 0) X(8, 4, 2, 0) X(16, 1, 8, 0) X(16, 2, 4, 0) X(16, 4, 2, 0) \
    X(32, 1, 8, 0) X(32, 2, 4, 0) X(32, 4, 2, 0) X(32, 8, 1, 0) X(32, 16, 1, 0) \
-   X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3) X(16, 2, 4, 3) X(32, 2, 4, 3)
+   X(16, 2, 8, 0) X(32, 2, 8, 0) X(8, 2, 4, 4) X(32, 4, 2, 3) X(16, 2, 4, 3) X(32, 2, 4, 3) X(16, 4, 2, 3)
 
 // The default tilings once more for calls whose K fills the tiling exactly (K = G*NV*16 bytes: every power of two
 // from 16 to 2048 floats, 8 to 1024 doubles): FLAG_EXACT_K drops the per-vector bounds predicates of every gather and
@@ -21,7 +21,7 @@ namespace fmm {
 // scale 24: chunk launch 30.5 ms against 25.8) and (8, 2, 4) at K = 64 floats (+1 %).
 #define FMM_FOR_EACH_EXACT_TILING(X) \
    X(4, 1, 4, 0) X(8, 1, 8, 0) X(16, 2, 4, 3) X(32, 2, 4, 0) X(32, 2, 8, 0) X(32, 2, 4, 3) \
-   X(32, 4, 2, 3) X(32, 8, 1, 0) X(32, 16, 1, 0)
+   X(32, 4, 2, 3) X(32, 8, 1, 0) X(32, 16, 1, 0) X(16, 4, 2, 3)
 
 // The default tilings with one-element vectors (FLAG_ELEMENT), for calls whose K, leading dimensions or base addresses
 // are not multiples of 16 bytes: K up to G*NV elements (512); 2-D / 3-D layouts (K = 2, 3) get 8 rows per warp.
