@@ -364,6 +364,10 @@ struct DeviceCtx {
    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_side_end = nullptr;
    cudaStream_t copy = nullptr;                 // copies finished blocks of Z back to the host while later blocks compute
    cudaEvent_t ev_block[8] = {};
+   // brings the column ids / edge values of the later blocks of such a call to the device while earlier blocks compute
+   // and go back (the two directions of the link at once)
+   cudaStream_t copy_in = nullptr;
+   cudaEvent_t ev_in[8] = {}, ev_inputs = nullptr;
    int sm_count = 148;
    DevBuf stage[7];  // val, indx, pntrb, pntre, x, y, z
    DevBuf counter, hub_row, hub_base, partials;
@@ -383,7 +387,7 @@ struct DeviceCtx {
 
 struct Options {
    int64_t beta_mode = 0, accept_vop_noop = 0, hub_chunk = 256, force_tiling = 0, force_generic = 0, warps_per_cta = 1,
-           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, chunk_order = 1, row_bins = 1, side_stream = 1, force_tiling_rows = 0,
+           engine = 0, edge_quantum = 256, stream_depth = 16, side_priority = 1, chunk_ctas_per_sm = 3, chunk_order = 1, row_bins = 1, blocked_inputs = 1, side_stream = 1, force_tiling_rows = 0,
            strict_udef = 0, multi_skip_empty_rows = 1, jit = 1, pdl = 1, timing_detail = 1, jit_call_shape = 0, jit_shape_mask = 3, offset32 = 1, exact_k = 1, element_vectors = 1, bulk_chunks = 0, bulk_warps = 8, bulk_ctas_per_sm = 0, hub_cap_initial = 1 << 16;
 };
 
@@ -463,6 +467,9 @@ int get_ctx(DeviceCtx **out)
       CK(cudaEventCreate(&c.ev_side_end));
       CK(cudaStreamCreateWithFlags(&c.copy, cudaStreamNonBlocking));
       for (auto &e : c.ev_block) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      CK(cudaStreamCreateWithFlags(&c.copy_in, cudaStreamNonBlocking));
+      for (auto &e : c.ev_in) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      CK(cudaEventCreateWithFlags(&c.ev_inputs, cudaEventDisableTiming));
       CK(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
       CKI(ensure_buf(c.counter, 256));
       CK(cudaMemset(c.counter.ptr, 0, 256));
@@ -763,6 +770,12 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
 
    long long h2d = 0, d2h = 0;
    const bool pe_is_pb1 = (static_cast<const char *>(a.pntre) == static_cast<const char *>(a.pntrb) + ps);
+   // A large Z that goes back to a host array is computed in blocks of rows (below).  With the usual (rowptr, rowptr+1)
+   // row pointers on the host the edges of a block are one slice of indx / val, so those arrays follow block by block:
+   // the slices of the later blocks come in while the earlier blocks compute and their rows of Z go out.
+   const bool blocked_out = !a.plan && !async && !on_dev[6] && !on_dev[2] && !on_dev[3] &&
+                            static_cast<size_t>(a.m) * a.k * es >= (static_cast<size_t>(32) << 20);
+   const bool defer_edges = blocked_out && pe_is_pb1 && t_opt.blocked_inputs != 0;
    if (!on_dev[2] || !on_dev[3]) {
       if (!on_dev[2] && !on_dev[3] && pe_is_pb1) {
          CKI(ensure_buf(c.stage[2], (a.m + 1) * ps));
@@ -794,15 +807,15 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
       }
       if (need_y && !on_dev[1]) {
          CKI(ensure_buf(c.stage[1], ext * is));
-         CK(cudaMemcpyAsync(c.stage[1].ptr, a.indx, ext * is, cudaMemcpyHostToDevice, st));
+         if (!defer_edges) CK(cudaMemcpyAsync(c.stage[1].ptr, a.indx, ext * is, cudaMemcpyHostToDevice, st));
          dv[1] = c.stage[1].ptr;
-         h2d += ext * is;
+         if (!defer_edges) h2d += ext * is;
       }
       if (need_val && !on_dev[0]) {
          CKI(ensure_buf(c.stage[0], ext * es));
-         CK(cudaMemcpyAsync(c.stage[0].ptr, a.val, ext * es, cudaMemcpyHostToDevice, st));
+         if (!defer_edges) CK(cudaMemcpyAsync(c.stage[0].ptr, a.val, ext * es, cudaMemcpyHostToDevice, st));
          dv[0] = c.stage[0].ptr;
-         h2d += ext * es;
+         if (!defer_edges) h2d += ext * es;
       }
    }
    const long long xbytes = need_x && a.m > 0 ? ((a.m - 1) * a.ldx + a.k) * es : 0;
@@ -1191,10 +1204,38 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
 
    // ---- Z goes back to a host array: copy it block of rows by block of rows while later blocks compute ----
    if (a.plan) CKI(ensure_buf(c.partials, static_cast<size_t>(std::max<long long>(a.plan->nchunks, 1)) * a.k * es));
-   if (!a.plan && !async && !on_dev[6] && !on_dev[2] && !on_dev[3] && static_cast<size_t>(a.m) * a.k * es >= (static_cast<size_t>(32) << 20)) {
+   if (blocked_out) {
       int64_t bounds[PIPE_BLOCKS + 1];
       CKI(a.ptr_bits == 64 ? shard_rows(a.m, PIPE_BLOCKS, static_cast<const int64_t *>(a.pntrb), static_cast<const int64_t *>(a.pntre), bounds)
                            : shard_rows(a.m, PIPE_BLOCKS, static_cast<const int32_t *>(a.pntrb), static_cast<const int32_t *>(a.pntre), bounds));
+      if (defer_edges) {
+         // the slices follow the dense inputs on the link, in block order; block b's kernels wait for slice b only
+         auto row_start = [&](int64_t r) -> long long {  // rowptr has m + 1 entries here (pntre == pntrb + 1)
+            return a.ptr_bits == 64 ? static_cast<long long>(static_cast<const int64_t *>(a.pntrb)[r])
+                                    : static_cast<long long>(static_cast<const int32_t *>(a.pntrb)[r]);
+         };
+         CK(cudaEventRecord(c.ev_inputs, st));
+         CK(cudaStreamWaitEvent(c.copy_in, c.ev_inputs, 0));
+         const bool in_idx = need_y && !on_dev[1], in_val = need_val && !on_dev[0];
+         const long long cap_e = std::min<long long>(in_idx ? static_cast<long long>(c.stage[1].bytes / is) : (1ll << 62),
+                                                     in_val ? static_cast<long long>(c.stage[0].bytes / es) : (1ll << 62));
+         for (int b = 0; b < PIPE_BLOCKS; b++) {
+            long long e0 = row_start(bounds[b]), e1 = row_start(bounds[b + 1]);
+            e0 = std::max<long long>(0, std::min(e0, cap_e));
+            e1 = std::max<long long>(e0, std::min(e1, cap_e));
+            if (e1 > e0 && in_idx) {
+               CK(cudaMemcpyAsync(static_cast<char *>(c.stage[1].ptr) + e0 * is, static_cast<const char *>(a.indx) + e0 * is, (e1 - e0) * is,
+                                  cudaMemcpyHostToDevice, c.copy_in));
+               h2d += (e1 - e0) * is;
+            }
+            if (e1 > e0 && in_val) {
+               CK(cudaMemcpyAsync(static_cast<char *>(c.stage[0].ptr) + e0 * es, static_cast<const char *>(a.val) + e0 * es, (e1 - e0) * es,
+                                  cudaMemcpyHostToDevice, c.copy_in));
+               h2d += (e1 - e0) * es;
+            }
+            CK(cudaEventRecord(c.ev_in[b], c.copy_in));
+         }
+      }
       // One block: its rows through the row scheduler (whole rows only on the first pass), then its part of Z back
       // to the host on the copy stream while the next block computes.
       auto run_block = [&](int b, bool with_rows) -> int {
@@ -1207,6 +1248,7 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
          if (q.x) q.x = p.x + r0 * p.ldx;
          q.z = p.z + r0 * p.ldz;
          q.counter = p.counter + 2 + b;  // words 0 and 1 belong to the unblocked passes
+         if (defer_edges && with_rows) CK(cudaStreamWaitEvent(st, c.ev_in[b], 0));  // first pass: this block's slice has arrived
          CKI(enqueue_pass(q, with_rows, false));
          CK(cudaEventRecord(c.ev_block[b], st));
          CK(cudaStreamWaitEvent(c.copy, c.ev_block[b], 0));
@@ -2068,6 +2110,7 @@ static int64_t *option_slot(const char *name)
    if (!strcmp(name, "chunk_ctas_per_sm")) return &g_opt.chunk_ctas_per_sm;
    if (!strcmp(name, "chunk_order")) return &g_opt.chunk_order;
    if (!strcmp(name, "row_bins")) return &g_opt.row_bins;
+   if (!strcmp(name, "blocked_inputs")) return &g_opt.blocked_inputs;
    if (!strcmp(name, "strict_udef")) return &g_opt.strict_udef;
    if (!strcmp(name, "multi_skip_empty_rows")) return &g_opt.multi_skip_empty_rows;
    if (!strcmp(name, "jit")) return &g_opt.jit;

@@ -415,6 +415,9 @@ int fusedmm_b200_check_csr(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_
  *                    (fusedmm_b200/csrc/fusedmm_bulk.cuh; the four optimised messages only).  Same results; measured
  *                    15 % to 2.4x slower on the benchmark configurations.  "bulk_warps" (1..8, default 8): warps per
  *                    block of that launch; "bulk_ctas_per_sm" (0 = as many as fit).
+ *   "blocked_inputs" 1 (default): in a call whose Z (32 MB or more) goes back to a host array block of rows by block of rows,
+ *                    host column ids and edge values given with (rowptr, rowptr + 1) row pointers come in block by block
+ *                    as well, behind the dense inputs, while earlier blocks compute and go out; 0: all inputs first.
  *   "offset32"       1 (default): with 32-bit column ids and rows of Y less than 2^32 bytes apart, the whole-row launch
  *                    of calls with 68..128 floats (34..64 doubles) per row runs the instantiation that forms a neighbour
  *                    row's address with one 32 x 32 + 64-bit multiply-add (bit-identical results; 4 % faster at

@@ -388,6 +388,17 @@ def test_scratch_growth_in_the_blocked_copy_back_does_not_accumulate_twice(cuda_
     assert st == 0 and info.hub_rows == hubs.size
     assert info.kernel_launches > 8 * 4          # 8 blocks, and the split rows of the blocks that overflowed again
     assert rel_err(z, want) <= 1e-4
+    # column ids and edge values came in block by block behind Y (the default); all inputs first gives the same Z
+    # and moves the same bytes
+    api.set_option("blocked_inputs", 0)
+    try:
+        z2 = z0.copy()
+        st2 = api.fusedMM_csr(M.MSG_SPMM, m, n, k, 1.0, 0, m, n, val, indx, rowptr[:-1], rowptr[1:], None, k, y, k, 1.0, z2, k)
+        info2 = api.call_info()
+    finally:
+        api.set_option("blocked_inputs", 1)
+    assert st2 == 0 and np.array_equal(z, z2)
+    assert info.h2d_bytes == info2.h2d_bytes == rowptr.nbytes + indx.nbytes + val.nbytes + y.nbytes + z0.nbytes
 
 
 def test_one_process_drives_several_gpus_from_threads(cuda_device, oracle):
