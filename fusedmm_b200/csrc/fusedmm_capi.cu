@@ -1214,12 +1214,14 @@ int run_typed(DeviceCtx &c, const HostArgs &a, const Decoded &d, const fusedmm_b
             return a.ptr_bits == 64 ? static_cast<long long>(static_cast<const int64_t *>(a.pntrb)[r])
                                     : static_cast<long long>(static_cast<const int32_t *>(a.pntrb)[r]);
          };
+         // (the first slice does not wait for them: it shares the link with the dense inputs, so the first block can
+         // start the moment those have arrived)
          CK(cudaEventRecord(c.ev_inputs, st));
-         CK(cudaStreamWaitEvent(c.copy_in, c.ev_inputs, 0));
          const bool in_idx = need_y && !on_dev[1], in_val = need_val && !on_dev[0];
          const long long cap_e = std::min<long long>(in_idx ? static_cast<long long>(c.stage[1].bytes / is) : (1ll << 62),
                                                      in_val ? static_cast<long long>(c.stage[0].bytes / es) : (1ll << 62));
          for (int b = 0; b < PIPE_BLOCKS; b++) {
+            if (b == 1) CK(cudaStreamWaitEvent(c.copy_in, c.ev_inputs, 0));
             long long e0 = row_start(bounds[b]), e1 = row_start(bounds[b + 1]);
             e0 = std::max<long long>(0, std::min(e0, cap_e));
             e1 = std::max<long long>(e0, std::min(e1, cap_e));
