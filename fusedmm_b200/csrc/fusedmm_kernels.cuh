@@ -315,6 +315,10 @@ __device__ __forceinline__ float  fmm_sqrt(float v)  { return sqrtf(v); }
 __device__ __forceinline__ double fmm_sqrt(double v) { return sqrt(v); }
 __device__ __forceinline__ float  fmm_log2(float v)  { return log2f(v); }
 __device__ __forceinline__ double fmm_log2(double v) { return log2(v); }
+// log2(1 + v) without forming 1 + v: for the small v that near-equal rows give (K = 1 or 2 layouts), 1 + v in float
+// keeps only a few digits of v and the logarithm inherits that error (2e-4 relative at v = 3e-4)
+__device__ __forceinline__ float  fmm_log2_1p(float v)  { return log1pf(v) * 1.44269504088896340736f; }
+__device__ __forceinline__ double fmm_log2_1p(double v) { return log1p(v) * 1.44269504088896340736; }
 
 template <typename T>
 __device__ __forceinline__ T sop_udef(T s, int kind, T p0, T p1, T p2, const T *table)
@@ -338,7 +342,7 @@ __device__ __forceinline__ T sop_udef(T s, int kind, T p0, T p1, T p2, const T *
          T v = T(-2) / (T(1) + s);
          return v > T(5) ? T(5) : (v < T(-5) ? T(-5) : v);
       }
-      case SOPK_LL: return fmm_log2(T(1) + fmm_sqrt(s));
+      case SOPK_LL: return fmm_log2_1p(fmm_sqrt(s));
       case SOPK_FA: return fmm_sqrt(s) + T(1) / s;
       case SOPK_AFFINE_RECIP: {
          T v = p0 / (p1 + s);

@@ -284,11 +284,12 @@ int fusedmm_b200_csr_static_scratch(int32_t dtype, int32_t ptr_bits, int32_t idx
  *
  * fusedmm_b200_plan_create copies host CSR arrays to the current device once (device arrays are
  * borrowed: keep them alive and unchanged while the plan lives), finds the rows that have to be split and
- * keeps that list.  val may be NULL (val_dtype ignored) for graphs used only with messages that do not
+ * keeps that list; for large graphs it also sorts the pieces of the split rows by column and the other rows by
+ * length inside windows (options "chunk_order", "row_bins": the values in force when the plan is made).  val may be NULL (val_dtype ignored) for graphs used only with messages that do not
  * read edge values; val_dtype: 0 float, 1 double.  nnz is ignored (the extent is the largest row end).
  * fusedmm_b200_plan_csr is fusedmm_b200_csr without the CSR arguments: x, y, z may be host or device
- * arrays, stream as in fusedmm_b200_csr.  Per call it saves the scan launch and, for host callers, the copy
- * of the column ids and edge values.  A plan belongs to the device it was created on.
+ * arrays, stream as in fusedmm_b200_csr.  Per call it saves the scan and the sort launches (three launches instead
+ * of eight on a large graph) and, for host callers, the copy of the column ids and edge values.  A plan belongs to the device it was created on.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct fusedmm_b200_plan fusedmm_b200_plan;
 int fusedmm_b200_plan_create(int32_t ptr_bits, int32_t idx_bits, int64_t m, int64_t nnz, const void *indx,

@@ -1,6 +1,7 @@
 """Seeded fuzzing of the C ABI against the CPU oracle: random messages (every valid stage code), shapes down to
 one row / one column / no edges at all, padded leading dimensions, all index-width combinations, both value
-types, both schedulers, all engines, host and device arrays, beta 0 and 1."""
+types, both schedulers, all engines, host and device arrays, beta 0 and 1, the sorted work orders of large graphs
+forced on and off."""
 import numpy as np
 import pytest
 
@@ -21,7 +22,7 @@ def one_case(rng, device, oracle, case):
     import torch
     vt = np.float32 if rng.random() < 0.6 else np.float64
     pt, it = [(np.int32, np.int32), (np.int64, np.int64), (np.int64, np.int32)][rng.integers(3)]
-    m = int(rng.choice([1, 2, 7, 33, 150, 600]))
+    m = int(rng.choice([1, 2, 7, 33, 150, 600, 2500]))
     n = int(rng.choice([1, 3, 40, 500]))
     k = int(rng.choice([1, 2, 3, 4, 8, 12, 16, 20, 32, 48, 64, 100, 128, 132, 256, 260]))
     pad = int(rng.choice([0, 0, 4, 5]))
@@ -52,8 +53,11 @@ def one_case(rng, device, oracle, case):
     use_stream_engine = contiguous and rng.random() < 0.5
     host = rng.random() < 0.35
     element_vectors = int(rng.random() < 0.6)   # rows that are not 16-byte granular: one-element vectors, or the element-strided engine
+    sorts = 2 * (case % 2)   # chunks in column order and whole rows sorted by length: forced on every other case, else off
     api.set_option("engine", 2 if use_stream_engine else 0)
     api.set_option("element_vectors", element_vectors)
+    api.set_option("chunk_order", sorts)
+    api.set_option("row_bins", sorts)
     try:
         if host:
             z = z0.copy()
@@ -76,8 +80,10 @@ def one_case(rng, device, oracle, case):
     finally:
         api.set_option("engine", 0)
         api.set_option("element_vectors", 1)
+        api.set_option("chunk_order", 1)
+        api.set_option("row_bins", 1)
     tag = (case, hex(msg), m, n, k, (ldx, ldy, ldz), vt.__name__, pt.__name__, it.__name__, sop, beta, hub, contiguous,
-           use_stream_engine, host)
+           use_stream_engine, host, sorts)
     assert st == st_o == 0, tag
     assert np.array_equal(z[:, k:], z0[:, k:]), tag   # padding columns untouched
     if np.isfinite(want[:, :k]).all():
