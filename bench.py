@@ -225,7 +225,8 @@ def cpu_leg(torch, eng, cfg, csr, x, z_gpu, nnz, flops_per_edge, target_s, steps
     return out
 
 
-def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n, k, nnz, r0, r1, flops_per_edge, barrier):
+def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n, k, nnz, r0, r1, flops_per_edge, barrier,
+                bounds=None, pz=None):
     """The same call through the synchronous typed entry point with pinned HOST arrays: all copies inside."""
     e2e_steps = args.e2e_steps or (3 if nnz > 200_000_000 else max(3, min(args.steps, 8)))
 
@@ -248,10 +249,36 @@ def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n,
         return {"value": None, "unit": "GFLOP/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None,
                 "skipped": f"{world} ranks x {need / 2**30:.1f} GiB of pinned host copies do not fit this node's free memory"}, True
     hv, hi, hp, hx = pinned(csr.val), pinned(csr.indx), pinned(csr.rowptr), pinned(x)
-    hz = torch.zeros((r1 - r0, k), dtype=tdtype, pin_memory=True)
     hpb, hpe = hp[:-1], hp[1:]
 
+    # N > 1: the ranks' PCIe links work side by side (fusedmm_b200.dist.HostStep): a rank brings 1/N of Y and its own
+    # shard of the graph, one all-gather over NVLink completes Y, its rows of Z go back
+    hs = None
+    if world > 1 and bounds is not None:
+        from fusedmm_b200 import dist as fdist
+        uses_val = ((msg >> 4) & 0xF) == 0 and ((msg >> 12) & 0xF) != 0
+        hs = fdist.HostStep(n, k, tdtype, dev, dist, bounds, nnz_max=int(hp[r1] - hp[r0]), with_val=uses_val,
+                            idx_dtype=csr.indx.dtype, pz=pz)
+    za, zb = hs.out_rows() if hs is not None else (r0, r1)
+    hz = torch.zeros((zb - za, k), dtype=tdtype, pin_memory=True)
+    z_ref = None
+    if hs is not None and pz is not None:  # the timed steps left the whole result in every rank's Z: keep this rank's
+        z_ref = pz.z[za:zb].clone()        # output rows for the comparison and make the rest of Z garbage
+        barrier()
+        pz.z.fill_(-12345.0)
+        barrier()
+
+    class _Bytes:
+        h2d_bytes = d2h_bytes = 0
+
     def e2e_step():
+        if hs is not None:
+            st = hs.step(msg, hp, hi, hv if hs._with_val else None, hx, hx, hz, sop=sop if sop is not None else 0,
+                         stream=torch.cuda.current_stream().cuda_stream, z_rows_only=True)
+            assert st == 0 and api.lib().fusedmm_b200_stream_status() == 0, api.status_string(st)
+            b = _Bytes()
+            b.h2d_bytes, b.d2h_bytes = hs.h2d_bytes, hs.d2h_bytes
+            return b
         st = api.fusedMM_csr(msg, r1 - r0, n, k, 1.0, nnz, n, n, hv, hi, hpb[r0:], hpe[r0:], hx[r0:], k, hx, k, 0.0,
                              hz, k, sop=sop if sop is not None else 0)
         assert st == 0, api.status_string(st)
@@ -270,15 +297,30 @@ def measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n,
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
+    nbytes = torch.tensor([float(einfo.h2d_bytes), float(einfo.d2h_bytes)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)  # bytes of the whole job, like the metric
     e2e = {"value": flops_per_edge * nnz / (e2e_ms * 1e-3) * 1e-9, "unit": "GFLOP/s",
-           "h2d_bytes_per_step": int(einfo.h2d_bytes), "d2h_bytes_per_step": int(einfo.d2h_bytes),
+           "h2d_bytes_per_step": int(nbytes[0].item()), "d2h_bytes_per_step": int(nbytes[1].item()),
            "ms_per_step": e2e_ms, "steps": e2e_steps,
            "timer": "host clock around the synchronous call (copies + kernels), max over ranks",
            "note": "per rank: its CSR rows' pointers, all column ids, X rows and all of Y in; its Z rows out"}
-    if world > 1:
+    if hs is not None:
+        e2e["note"] = ("fusedmm_b200.dist.HostStep, bytes summed over the ranks: every rank brings 1/N of the rows of Y and the row "
+                       "pointers and column ids of its own row shard over its own PCIe link, one in-place all-gather over "
+                       "NVLink completes Y on every GPU, the rank's kernels run on device arrays"
+                       + (" and store every finished row into the Z of the rank that copies it out, and every rank copies 1/N "
+                          "of the rows of Z back to the host" if pz is not None else ", its rows of Z go back to the host"))
+    elif world > 1:
         e2e["note"] += ("; with N ranks every rank stages all of Y over its own PCIe link in the same interval, so this "
                         "figure does not scale with N: it is a one-GPU figure")
     e2e_ok = bool(torch.isfinite(hz).all())
+    if z_ref is not None:
+        same = torch.tensor([1.0 if torch.equal(hz.to(dev), z_ref) else 0.0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        e2e["host_z_equals_device_resident_z_on_every_rank"] = bool(same.item() == 1.0)
+        e2e_ok = e2e_ok and e2e["host_z_equals_device_resident_z_on_every_rank"]
+        return e2e, e2e_ok
 
     # the same with the graph kept on the device by a plan (inspector/executor split): per step only X(=Y) goes
     # in and Z comes out; reported beside the headline figure, which stays the plain fusedMM_csr call
@@ -551,7 +593,7 @@ def bench_gpu(args, ctx, cfgname, dtype, scale, steps, warmup, with_e2e, cpu_tar
     e2e, e2e_ok = None, True
     if with_e2e:
         e2e, e2e_ok = measure_e2e(args, api, torch, dist, world, dev, csr, x, tdtype, msg, sop, n, k, nnz, r0, r1,
-                                  flops_per_edge, barrier)
+                                  flops_per_edge, barrier, bounds=bounds, pz=pz)
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu_baseline = None

@@ -135,3 +135,138 @@ def fusedMM_csr_fused_exchange(imessage, n, k, val, indx, rowptr, x, y, pz: Peer
                              z_multicast=pz.multicast_at_row(r0) if pz.use_multicast() else None)
     pz.finish_step()
     return st
+
+
+class HostStep:
+    """The step for callers whose arrays live in HOST memory while N GPUs share the work (every rank sees the same
+    host arrays, or its own copy of them).  A rank that called ``fusedMM_csr`` with host arrays would bring all of Y
+    over its own PCIe link, N times the same bytes per node and per step.  Here the links work side by side and
+    NVLink does the rest:
+
+    1. rank r copies rows ``[r*n/N, (r+1)*n/N)`` of Y, and of the graph only the row pointers and column ids
+       (edge values) of its own row shard, to its GPU;
+    2. one all-gather (in place, over NVLink) completes Y on every GPU;
+    3. the rank's kernels compute its row shard of Z (shards of equal COST, ``bounds``) from device arrays;
+    4. the rank copies rows of Z back to the host array: without ``pz`` its own shard; with ``pz`` (a ``PeerZ``) the
+       rows ``[r*m/N, (r+1)*m/N)``, equal BYTES per link: the kernels store every finished row that has edges
+       straight into the Z of the one rank that will copy it out (a row crosses NVLink at most once; rows without
+       edges are zeroed by the receiver from the row pointers of its range).
+
+    ``compute`` is the call that does step 3 (``api.fusedMM_csr`` with device tensors); the CPU tests pass a stand-in,
+    so that slicing, re-basing and the all-gather are covered with the ``gloo`` backend."""
+
+    def __init__(self, n, k, dtype, device, dist, bounds, nnz_max=None, with_val=False, idx_dtype=None, group=None,
+                 compute=None, pz=None, m=None):
+        import torch
+        self._torch, self.dist, self.group = torch, dist, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.n, self.k = int(n), int(k)
+        self.m = int(m) if m is not None else int(n)
+        self.r0, self.r1 = int(bounds[self.rank]), int(bounds[self.rank + 1])
+        self.rows_per = (self.n + self.world - 1) // self.world
+        self.zrows_per = (self.m + self.world - 1) // self.world
+        self.y = torch.empty((self.rows_per * self.world, self.k), dtype=dtype, device=device)
+        self.pz = pz if (pz is not None and self.world > 1) else None
+        self.z = None if self.pz is not None else torch.zeros((max(self.r1 - self.r0, 1), self.k), dtype=dtype, device=device)
+        self.rowptr = torch.empty(self.r1 - self.r0 + 1, dtype=torch.int64, device=device)
+        self.rowptr_out = torch.empty(self.zrows_per + 1, dtype=torch.int64, device=device) if self.pz is not None else None
+        self.idx_dtype = idx_dtype or torch.int32
+        self.indx = self.val = None
+        self._nnz_cap = 0
+        self._with_val = with_val
+        self._dtype, self._device = dtype, device
+        if nnz_max:
+            self._reserve(int(nnz_max))
+        self.compute = compute or api.fusedMM_csr
+        self.h2d_bytes = self.d2h_bytes = 0
+
+    def out_rows(self):
+        """Rows of Z this rank copies to the host in a step."""
+        if self.pz is None:
+            return self.r0, self.r1
+        a = min(self.m, self.rank * self.zrows_per)
+        return a, min(self.m, a + self.zrows_per)
+
+    def _reserve(self, edges):
+        if edges > self._nnz_cap:
+            torch = self._torch
+            self.indx = torch.empty(edges, dtype=self.idx_dtype, device=self._device)
+            self.val = torch.empty(edges, dtype=self._dtype, device=self._device) if self._with_val else None
+            self._nnz_cap = edges
+
+    def step(self, imessage, rowptr_host, indx_host, val_host, x_host, y_host, z_host, sop=None, stream=None,
+             z_rows_only=False):
+        """One call: ``rowptr_host`` (m+1 int64 entries), ``indx_host``, ``val_host`` (or None), ``x_host``
+        (``y_host`` itself when X and Y are the same matrix), ``y_host`` and ``z_host`` are host tensors (pinned for
+        speed).  Returns the status of the compute calls; the rows ``out_rows()`` of ``z_host`` are complete on return
+        (``z_rows_only``: ``z_host`` holds just those rows).  Every rank of the group must call it."""
+        torch = self._torch
+        r0, r1, k, n = self.r0, self.r1, self.k, self.n
+        cuda = self.y.is_cuda
+        esz = self.y.element_size()
+        kw = {"stream": stream} if stream is not None else {}
+        h2d = 0
+        # 1. this rank's slice of Y, and its slice of the graph
+        a = self.rank * self.rows_per
+        b = min(n, a + self.rows_per)
+        if b > a:
+            self.y[a:b].copy_(y_host[a:b], non_blocking=True)
+            h2d += (b - a) * k * esz
+        e0, e1 = int(rowptr_host[r0]), int(rowptr_host[r1])
+        self._reserve(max(e1 - e0, 1))
+        self.rowptr.copy_(rowptr_host[r0:r1 + 1], non_blocking=True)
+        self.rowptr.sub_(e0)  # the slice of column ids starts at 0 on the device
+        h2d += (r1 - r0 + 1) * 8
+        if e1 > e0:
+            self.indx[:e1 - e0].copy_(indx_host[e0:e1], non_blocking=True)
+            h2d += (e1 - e0) * self.indx.element_size()
+            if self._with_val and val_host is not None:
+                self.val[:e1 - e0].copy_(val_host[e0:e1], non_blocking=True)
+                h2d += (e1 - e0) * self.val.element_size()
+        za, zb = self.out_rows()
+        if self.pz is not None and zb > za:  # the row pointers of the rows this rank copies out: their empty rows become 0 here
+            self.rowptr_out[:zb - za + 1].copy_(rowptr_host[za:zb + 1], non_blocking=True)
+            h2d += (zb - za + 1) * 8
+        # 2. all ranks' slices of Y, in place
+        if self.world > 1:
+            mine = self.y[a:a + self.rows_per].reshape(-1)
+            # NCCL gathers in place (the input is this rank's slot of the output); other backends get a copy
+            self.dist.all_gather_into_tensor(self.y.view(-1), mine if cuda else mine.clone(), group=self.group)
+        # 3. the row shard
+        if x_host is y_host:
+            x_dev = self.y[r0:]
+        else:
+            x_dev = torch.empty((max(r1 - r0, 1), k), dtype=self.y.dtype, device=self.y.device)
+            if r1 > r0:
+                x_dev[:r1 - r0].copy_(x_host[r0:r1], non_blocking=True)
+                h2d += (r1 - r0) * k * esz
+        st = 0
+        if self.pz is None:
+            if r1 > r0:
+                st = self.compute(imessage, r1 - r0, n, k, 1.0, e1 - e0, n, n, self.val, self.indx, self.rowptr[:-1],
+                                  self.rowptr[1:], x_dev, k, self.y, k, 0.0, self.z, k, sop=sop, **kw)
+                # 4. its rows of Z back to the host
+                (z_host[:r1 - r0] if z_rows_only else z_host[r0:r1]).copy_(self.z[:r1 - r0], non_blocking=True)
+        else:
+            pz = self.pz
+            if zb > za:
+                st = api.zero_empty_rows(self.rowptr_out[:zb - za], self.rowptr_out[1:zb - za + 1], pz.z[za:], k, k,
+                                         stream=stream)
+            # one call per rank whose output range this shard reaches into: rows [lo, hi) go to rank d's Z
+            for d in range(self.world):
+                lo, hi = max(r0, d * self.zrows_per), min(r1, (d + 1) * self.zrows_per, self.m)
+                if hi <= lo or st != 0:
+                    continue
+                edges = int(rowptr_host[hi]) - int(rowptr_host[lo])
+                st = self.compute(imessage, hi - lo, n, k, 1.0, edges, n, n, self.val, self.indx,
+                                  self.rowptr[lo - r0:-1], self.rowptr[lo - r0 + 1:], x_dev[lo - r0:], k, self.y, k, 0.0,
+                                  pz.z[lo:], k, sop=sop,
+                                  z_peers=None if d == self.rank else [pz.ptrs[d] + lo * pz.row_bytes], **kw)
+            pz.finish_step()  # every rank's kernels, and with them their stores into this rank's Z, are done
+            if zb > za:
+                (z_host[:zb - za] if z_rows_only else z_host[za:zb]).copy_(pz.z[za:zb], non_blocking=True)
+            pz.finish_step()  # nobody stores into a Z that is still being copied out
+        if cuda:
+            torch.cuda.current_stream().synchronize()
+        self.h2d_bytes, self.d2h_bytes = h2d, (zb - za) * k * esz
+        return st
