@@ -241,9 +241,12 @@ class HostStep:
                 x_dev[:r1 - r0].copy_(x_host[r0:r1], non_blocking=True)
                 h2d += (r1 - r0) * k * esz
         st = 0
+        # nnz is the library's hint for scratch sizes and for the length at which rows are split: the whole graph's
+        # count everywhere, so that a row is cut (and its pieces added) the same way whatever the sharding
+        nnz_hint = int(rowptr_host[self.m]) - int(rowptr_host[0])
         if self.pz is None:
             if r1 > r0:
-                st = self.compute(imessage, r1 - r0, n, k, 1.0, e1 - e0, n, n, self.val, self.indx, self.rowptr[:-1],
+                st = self.compute(imessage, r1 - r0, n, k, 1.0, nnz_hint, n, n, self.val, self.indx, self.rowptr[:-1],
                                   self.rowptr[1:], x_dev, k, self.y, k, 0.0, self.z, k, sop=sop, **kw)
                 # 4. its rows of Z back to the host
                 (z_host[:r1 - r0] if z_rows_only else z_host[r0:r1]).copy_(self.z[:r1 - r0], non_blocking=True)
@@ -257,8 +260,7 @@ class HostStep:
                 lo, hi = max(r0, d * self.zrows_per), min(r1, (d + 1) * self.zrows_per, self.m)
                 if hi <= lo or st != 0:
                     continue
-                edges = int(rowptr_host[hi]) - int(rowptr_host[lo])
-                st = self.compute(imessage, hi - lo, n, k, 1.0, edges, n, n, self.val, self.indx,
+                st = self.compute(imessage, hi - lo, n, k, 1.0, nnz_hint, n, n, self.val, self.indx,
                                   self.rowptr[lo - r0:-1], self.rowptr[lo - r0 + 1:], x_dev[lo - r0:], k, self.y, k, 0.0,
                                   pz.z[lo:], k, sop=sop,
                                   z_peers=None if d == self.rank else [pz.ptrs[d] + lo * pz.row_bytes], **kw)

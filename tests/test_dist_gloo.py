@@ -101,7 +101,7 @@ def _host_step_worker(rank, world, port, tmp):
                          tx, ty, z_host, sop=sop)
             assert st == 0
             # the stand-in saw re-based row pointers (first edge 0) and exactly this shard's edges
-            assert calls[-1] == (r1 - r0, int(rowptr[r1] - rowptr[r0]), 0, int(rowptr[r1] - rowptr[r0]))
+            assert calls[-1] == (r1 - r0, int(rowptr[-1]), 0, int(rowptr[r1] - rowptr[r0]))   # nnz: the whole graph's, a hint
             assert torch.equal(hs.y[:n], ty)                      # all of Y arrived through the all-gather
             want = np.zeros((m, k), np.float32)
             orc.csr(msg, m, n, k, val, indx, rowptr[:-1].copy(), rowptr[1:].copy(), y if same else x_other, k, y, k, 0.0,
