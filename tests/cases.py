@@ -73,7 +73,7 @@ def within_tolerance(z, want, tol, exact_fn, k=None, slack=4.0):
     """Acceptance of a GPU result `z` against the oracle's `want` (same precision).  Passes when they agree within
     `tol` in the metric of rel_err.  Messages that feed a cancelling reduction into a product or a reciprocal
     (signed inputs, s near 0 or near a pole of the scalar function) amplify the rounding of s in the oracle as much
-    as in the GPU kernel; for those the judge is a higher-precision evaluation of the same inputs, `exact_fn()`
+    as in the GPU kernel; for those the arbiter is a higher-precision evaluation of the same inputs, `exact_fn()`
     (called only when needed): the GPU result must be no further from it than `slack` times the oracle is, or
     `tol`.  Returns (ok, error vs the oracle, error vs exact or None, the oracle's error vs exact or None)."""
     e = rel_err(z, want, k)
