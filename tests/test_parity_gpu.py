@@ -812,6 +812,49 @@ def test_whole_rows_sorted_by_length_inside_windows(cuda_device, oracle, vt):
         api.set_option("row_bins", 1)
 
 
+def test_host_arrays_step_on_one_gpu(cuda_device, oracle, tmp_path):
+    """fusedmm_b200.dist.HostStep with a group of one rank: pinned host arrays in, the rank's slice of Y and of the graph
+    to the GPU, re-based row pointers, the library's call on device arrays, Z back to the host array; same bits as the
+    plain host-array call (the multi-rank parts are covered on CPU by tests/test_dist_gloo.py and on GPUs by bench.py)."""
+    import torch
+    import torch.distributed as dist
+    from fusedmm_b200 import dist as fdist
+    own_group = not dist.is_initialized()
+    if own_group:
+        dist.init_process_group("gloo", init_method=f"file://{tmp_path}/rendezvous", rank=0, world_size=1)
+    try:
+        rng = np.random.default_rng(81)
+        m = n = 1500
+        k = 128
+        pntrb, pntre, indx, val = random_csr(rng, m, n, 8, np.int64, np.int32, hub=900)
+        rowptr = np.concatenate([pntrb, pntre[-1:]])
+        val = val.astype(np.float32)
+        y = np.nan_to_num(dense(rng, n, k, k, np.float32))
+        x_other = np.nan_to_num(dense(rng, m, k, k, np.float32))
+        bounds = fdist.shard_bounds(rowptr, 1)
+        for msg, sop, same, with_val in ((M.MSG_SIGMOID, M.SOP_SIGMOID, True, False), (M.MSG_SPMM, 0, False, True),
+                                        (M.MSG_TDIST, M.SOP_FR, True, False)):
+            hs = fdist.HostStep(n, k, torch.float32, cuda_device, dist, bounds, with_val=with_val)
+            ty = torch.from_numpy(y).pin_memory()
+            tx = ty if same else torch.from_numpy(x_other).pin_memory()
+            z_host = torch.full((m, k), -777.0).pin_memory()
+            with torch.cuda.device(cuda_device):
+                st = hs.step(msg, torch.from_numpy(rowptr), torch.from_numpy(indx), torch.from_numpy(val) if with_val else None,
+                             tx, ty, z_host, sop=sop)
+            assert st == 0 and hs.out_rows() == (0, m)
+            assert hs.d2h_bytes == m * k * 4 and hs.h2d_bytes >= n * k * 4 + (m + 1) * 8 + indx.nbytes
+            zd = np.zeros((m, k), np.float32)
+            assert api.fusedMM_csr(msg, m, n, k, 1.0, int(rowptr[-1]), m, n, val, indx, rowptr[:-1], rowptr[1:],
+                                   y if same else x_other, k, y, k, 0.0, zd, k, sop=sop) == 0
+            assert np.array_equal(z_host.numpy(), zd), hex(msg)
+            want = np.zeros((m, k), np.float32)
+            assert oracle.csr(msg, m, n, k, val, indx, pntrb, pntre, y if same else x_other, k, y, k, 0.0, want, k, sop_kind=sop) == 0
+            assert rel_err(zd, want) <= 1e-4
+    finally:
+        if own_group:
+            dist.destroy_process_group()
+
+
 def test_async_stream_entry(cuda_device, oracle):
     import torch
     rng = np.random.default_rng(10)
