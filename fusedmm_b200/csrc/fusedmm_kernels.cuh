@@ -483,7 +483,7 @@ struct VecEngine {
          inb[v] = EXACT_K || e0 < p.k;
 #pragma unroll
          for (int i = 0; i < W; i++) { xv[v][i] = T(0); acc[v][i] = aop_identity<T>(aop); }
-         if (need_x && inb[v]) ld_vec(p.x + w.row * p.ldx + e0, xv[v]);
+         if (need_x && inb[v] && w.eb < w.ee) ld_vec(p.x + w.row * p.ldx + e0, xv[v]);  // an item without edges reads nothing
       }
 
       // Gather buffers, zeroed once: vectors past the end of the row (K < G*NV*W) are never loaded
@@ -660,6 +660,7 @@ fused_vec_kernel(const Params<T> p)
       }
       T acc[NV][W];
       Eng::template run<true>(p, w, lane, acc);
+      if (mine && p.accumulate && w.eb == w.ee) mine = false;  // accumulating nothing: the row of Z stays as it is
       if (mine) {
          T *dst = p.z + w.row * p.ldz;
 #pragma unroll
@@ -701,7 +702,7 @@ fused_vec_kernel(const Params<T> p)
       T acc[NV][W];
       Eng::template run<false>(p, w, lane, acc);
 
-      if (lane < G) {  // slot 0 holds (like every slot) the finished sums
+      if (lane < G && !(w.dst_item < 0 && p.accumulate && w.eb == w.ee)) {  // slot 0 holds (like every slot) the finished sums
          const bool to_z = w.dst_item < 0;
          const bool remote = !(p.skip_empty_remote && w.eb == w.ee);
          T *dst = to_z ? p.z + w.row * p.ldz : p.partials + w.dst_item * p.k;
