@@ -197,3 +197,16 @@ def test_shard_rows_with_a_row_weight_balances_rows_plus_edges(lib):
     # no edges at all: rows alone are balanced
     b = api.shard_rows(np.zeros(10, np.int32), np.zeros(10, np.int32), 5, row_weight=1)
     assert list(b) == [0, 2, 4, 6, 8, 10]
+
+
+def test_every_option_is_documented_in_the_header():
+    """Every option name the library accepts (fusedmm_b200_set_option / FUSEDMM_B200_OPTIONS) has its paragraph in
+    include/fusedmm_b200.h."""
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    src = (root / "fusedmm_b200" / "csrc" / "fusedmm_capi.cu").read_text()
+    hdr = (root / "include" / "fusedmm_b200.h").read_text()
+    names = re.findall(r'!strcmp\(name, "([a-z_0-9]+)"\)', src)
+    assert len(names) >= 25
+    assert [n for n in names if f'"{n}"' not in hdr] == []
